@@ -1,0 +1,138 @@
+/*
+ * C ABI of the B200 anchor-attention prefill operator.
+ *
+ * One shared library (libanchor_attn_b200.so), plain C symbols, raw device
+ * pointers and sizes.  Nothing here allocates or synchronises unless stated:
+ * every entry point enqueues kernels on the caller's CUDA stream and returns.
+ * The caller owns every buffer.  Two calls may run concurrently on different
+ * streams as long as they use different workspaces.
+ *
+ * Citations are paths inside the reference project (yuzhouzhang9/Anchor-Attention).
+ * The reference has no FFI of its own: its operator is a Python function that
+ * launches three Triton kernels.  Each entry point below names the Python
+ * function whose work it replaces.
+ */
+#ifndef ANCHOR_ATTN_B200_H
+#define ANCHOR_ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error codes (0 = success).  aa_strerror() gives the text. */
+enum {
+    AA_OK = 0,
+    AA_ERR_NULL = -1,          /* a required pointer is NULL                         */
+    AA_ERR_SHAPE = -2,         /* B/H/Hkv/N non-positive, H % Hkv != 0               */
+    AA_ERR_HEAD_DIM = -3,      /* D != 128                                           */
+    AA_ERR_STEP = -4,          /* step not in {16, 32}  (anchor_attn_v4.py:305)      */
+    AA_ERR_BLOCK = -5,         /* block_size != 128 (the only size any harness uses) */
+    AA_ERR_SEQ = -6,           /* N % (block_size*step) != 0 (anchor_attn_v4.py:308) */
+    AA_ERR_WORKSPACE = -7,     /* workspace missing, misaligned or too small         */
+    AA_ERR_STRIDE = -8,        /* a stride is not a multiple of 8 elements (16 B)    */
+    AA_ERR_DTYPE = -9,         /* dtype is not AA_BF16                               */
+    AA_ERR_CUDA = -10,         /* a CUDA runtime/driver call failed (see aa_last_cuda_error) */
+    AA_ERR_DEVICE_TIMEOUT = -11,/* a bounded device-side wait gave up (status word)  */
+    AA_ERR_TOO_LARGE = -12     /* size beyond what an entry point supports           */
+};
+
+enum { AA_BF16 = 0 };
+
+/*
+ * Problem description.  Logical tensor shapes:
+ *   q, out : [B, H,   N, D]      k, v : [B, Hkv, N, D]
+ * Query head h reads KV head h / (H / Hkv), the order repeat_kv produces
+ * (my_utils/ops_util.py:6-24); pass Hkv == H for pre-expanded K/V, which is
+ * what the reference's caller does (modules/llama/anchor_attention.py:89-91).
+ * Strides are in ELEMENTS; the D axis must be contiguous (stride 1) and every
+ * other stride a multiple of 8 elements.  Any of [B,H,N,D] and [B,N,H,D]
+ * memory orders is therefore accepted without a copy.
+ */
+typedef struct aa_params {
+    int32_t B, H, Hkv, N, D;
+    int32_t block_size;        /* 128 (patch.py:36-40 "block_size_M")                    */
+    int32_t step;              /* 16 or 32 (patch.py:36-40 "step")                       */
+    int32_t dtype;             /* AA_BF16                                                */
+    float   theta;             /* "difference"/theta in natural-log units, default 12;
+                                  the library multiplies by log2(e) as anchor_attn_v4.py:298 does */
+    float   sm_scale;          /* 0 => D^-0.5 (anchor_attn_v4.py:312)                    */
+    const void *q, *k, *v;     /* device pointers, bf16                                  */
+    void       *out;           /* device pointer, bf16, same logical shape as q          */
+    int64_t q_stride_b, q_stride_h, q_stride_n;
+    int64_t k_stride_b, k_stride_h, k_stride_n;
+    int64_t v_stride_b, v_stride_h, v_stride_n;
+    int64_t o_stride_b, o_stride_h, o_stride_n;
+    void   *workspace;         /* device scratch, 256-byte aligned, >= aa_workspace_bytes() */
+    size_t  workspace_bytes;
+} aa_params_t;
+
+/* Where the inter-kernel state lives inside the workspace (byte offsets).
+ * Replaces the tensors the reference allocates per call: L_buffer, M_buffer,
+ * Acc_buffer (anchor_step_1_2_v2.py:174-176), true_coords, true_counts
+ * (get_mask_test.py:138-145).  The id lists are stored CSR-style with a static
+ * capacity: big block b of a head owns ids[id_row_offset(b) .. +counts[b]),
+ * id_row_offset(b) = sum_{b'<b} max(0, b'*G - 2*block_size), G = block_size*step,
+ * ids_per_head = id_row_offset(NB). */
+typedef struct aa_workspace_layout {
+    size_t m_off;        /* float   [B,H,N]          row maxima of step 1 (log2 domain)        */
+    size_t l_off;        /* float   [B,H,N]          softmax denominators of step 1             */
+    size_t acc_off;      /* float   [B,H,N,D]        un-normalised outputs of step 1            */
+    size_t qpool_off;    /* bf16    [B,H,N/bs,D]     block-mean queries                         */
+    size_t apool_off;    /* float   [B,H,N/bs]       block-mean anchors (bf16-valued)           */
+    size_t bitmap_off;   /* uint32  [B,H,NB,N/32]    hit bitmap of step 2                       */
+    size_t counts_off;   /* int32   [B,H,NB]         selected columns per big block             */
+    size_t ids_off;      /* int32   [B,H,ids_per_head] ascending selected column ids            */
+    size_t status_off;   /* int32   [4]              device status word(s), 0 = ok              */
+    size_t total_bytes;
+    int64_t ids_per_head;
+} aa_workspace_layout_t;
+
+/* Size and layout of the workspace for a problem (only the shape fields of p
+ * are read).  Host-only, no CUDA calls. */
+int aa_workspace_bytes(const aa_params_t *p, size_t *bytes);
+int aa_workspace_layout(const aa_params_t *p, aa_workspace_layout_t *layout);
+
+/* First id slot of big block b inside a head's id list (see above). */
+int64_t aa_id_row_offset(int32_t block_size, int32_t step, int32_t b);
+
+/* The whole operator: steps 1, 2, 3 back to back on `stream` (a cudaStream_t).
+ * Replaces anchor_attn -> _anchor_attn (anchor_attn_v4.py:291-324, 226-273). */
+int aa_forward(const aa_params_t *p, void *stream);
+
+/* Step 1, anchor / window attention: fills M, L, Acc in the workspace.
+ * Replaces anchor_attn_step_1 (anchor_step_1_2_v2.py:164-196). */
+int aa_step1_anchor(const aa_params_t *p, void *stream);
+
+/* Step 2, difference-aware stripe identification: reads q, k and M, fills
+ * qpool, apool, bitmap, counts and ids.  Replaces anchor_attn_step_2 ->
+ * get_q_mask (anchor_step_1_2_v2.py:199-210, get_mask_test.py:127-159). */
+int aa_step2_stripes(const aa_params_t *p, void *stream);
+
+/* Step 3, gathered sparse flash attention merged with the step-1 state:
+ * reads M, L, Acc, counts, ids; writes out.  Replaces the launch of
+ * _triton_stripe_sparse_attn_fwd_kernel_step3 (anchor_attn_v4.py:246-268). */
+int aa_step3_sparse(const aa_params_t *p, void *stream);
+
+/* Reads the device status word (synchronises the stream first).  Returns AA_OK
+ * or AA_ERR_DEVICE_TIMEOUT / AA_ERR_CUDA. */
+int aa_check_status(const aa_params_t *p, void *stream);
+
+/* Sum of all counts as computed by the last aa_step2_stripes on this
+ * workspace, written to *total (synchronises the stream).  The numerator of the
+ * reference's sparsity ratio (anchor_attn_v4.py:271). */
+int aa_total_selected(const aa_params_t *p, void *stream, int64_t *total);
+
+const char *aa_strerror(int code);
+/* Text of the last CUDA error this library saw on the calling thread. */
+const char *aa_last_cuda_error(void);
+/* Library version, and how many of the library's kernels one aa_forward enqueues. */
+int aa_version(void);
+int aa_launches_per_forward(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANCHOR_ATTN_B200_H */
