@@ -1,0 +1,78 @@
+"""ctypes binding of libanchor_attn_b200.so (the C ABI in include/anchor_attn_b200.h).
+
+The library is built in-tree by ``anchor_attention_b200.build``.  There is no
+fallback: if the library is missing or fails to load, importing the operator
+raises."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libanchor_attn_b200.so")
+
+AA_OK = 0
+AA_BF16 = 0
+
+EXPORTS = [
+    "aa_workspace_bytes", "aa_workspace_layout", "aa_id_row_offset", "aa_forward",
+    "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
+    "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
+    "aa_launches_per_forward",
+]
+
+
+class AAParams(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+        ("N", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("block_size", ctypes.c_int32), ("step", ctypes.c_int32), ("dtype", ctypes.c_int32),
+        ("theta", ctypes.c_double), ("sm_scale", ctypes.c_double),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("q_stride_b", ctypes.c_int64), ("q_stride_h", ctypes.c_int64), ("q_stride_n", ctypes.c_int64),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_h", ctypes.c_int64), ("k_stride_n", ctypes.c_int64),
+        ("v_stride_b", ctypes.c_int64), ("v_stride_h", ctypes.c_int64), ("v_stride_n", ctypes.c_int64),
+        ("o_stride_b", ctypes.c_int64), ("o_stride_h", ctypes.c_int64), ("o_stride_n", ctypes.c_int64),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
+class AALayout(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_size_t) for n in (
+        "m_off", "l_off", "acc_off", "qpool_off", "apool_off", "bitmap_off", "counts_off",
+        "ids_off", "status_off", "total_bytes")] + [("ids_per_head", ctypes.c_int64)]
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library once and declare the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m anchor_attention_b200.build` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(LIB_PATH)
+    P = ctypes.POINTER(AAParams)
+    lib.aa_workspace_bytes.argtypes = [P, ctypes.POINTER(ctypes.c_size_t)]
+    lib.aa_workspace_layout.argtypes = [P, ctypes.POINTER(AALayout)]
+    lib.aa_id_row_offset.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.aa_id_row_offset.restype = ctypes.c_int64
+    for name in ("aa_forward", "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status"):
+        getattr(lib, name).argtypes = [P, ctypes.c_void_p]
+        getattr(lib, name).restype = ctypes.c_int
+    lib.aa_total_selected.argtypes = [P, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
+    lib.aa_strerror.argtypes = [ctypes.c_int]
+    lib.aa_strerror.restype = ctypes.c_char_p
+    lib.aa_last_cuda_error.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+def error_text(code: int) -> str:
+    lib = load()
+    msg = lib.aa_strerror(code).decode()
+    if code == -10:
+        msg += ": " + lib.aa_last_cuda_error().decode()
+    return msg

@@ -1,0 +1,293 @@
+// C ABI of the anchor-attention operator: argument checks, workspace layout and
+// kernel launches.  Declarations and the reference functions each entry point
+// replaces are in include/anchor_attn_b200.h.
+#include "../../include/anchor_attn_b200.h"
+
+#include <stdio.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "attend_mma.cuh"
+#include "common.cuh"
+#include "stripe.cuh"
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+    return AA_ERR_CUDA;
+}
+
+size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+int check_shape(const aa_params_t* p) {
+    if (!p) return AA_ERR_NULL;
+    if (p->B <= 0 || p->H <= 0 || p->Hkv <= 0 || p->N <= 0 || p->H % p->Hkv != 0) return AA_ERR_SHAPE;
+    if (p->D != 128) return AA_ERR_HEAD_DIM;
+    if (p->step != 16 && p->step != 32) return AA_ERR_STEP;
+    if (p->block_size != 128) return AA_ERR_BLOCK;
+    if (p->N % (p->block_size * p->step) != 0) return AA_ERR_SEQ;
+    if (p->dtype != AA_BF16) return AA_ERR_DTYPE;
+    if ((int64_t)p->N * p->H * p->B > (int64_t)1 << 40) return AA_ERR_TOO_LARGE;
+    return AA_OK;
+}
+
+bool stride_ok(int64_t s) { return s % 8 == 0; }
+
+int check_full(const aa_params_t* p, aa_workspace_layout_t* lay) {
+    int rc = check_shape(p);
+    if (rc) return rc;
+    if (!p->q || !p->k || !p->v || !p->out) return AA_ERR_NULL;
+    const int64_t st[] = {p->q_stride_b, p->q_stride_h, p->q_stride_n, p->k_stride_b, p->k_stride_h, p->k_stride_n,
+                          p->v_stride_b, p->v_stride_h, p->v_stride_n, p->o_stride_b, p->o_stride_h, p->o_stride_n};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return AA_ERR_STRIDE;
+    if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->out) & 15) return AA_ERR_STRIDE;
+    rc = aa_workspace_layout(p, lay);
+    if (rc) return rc;
+    if (!p->workspace || ((uintptr_t)p->workspace & 255) || p->workspace_bytes < lay->total_bytes)
+        return AA_ERR_WORKSPACE;
+    return AA_OK;
+}
+
+aa::TensorView view(const void* ptr, int64_t sb, int64_t sh, int64_t sn) {
+    return aa::TensorView{static_cast<const __nv_bfloat16*>(ptr), sb, sh, sn};
+}
+
+double scale_of(const aa_params_t* p) { return p->sm_scale != 0.0 ? p->sm_scale : 1.0 / sqrt((double)p->D); }
+
+template <typename T>
+T* ws_ptr(const aa_params_t* p, size_t off) {
+    return reinterpret_cast<T*>(static_cast<uint8_t*>(p->workspace) + off);
+}
+
+aa::AttendArgs attend_args(const aa_params_t* p, const aa_workspace_layout_t& lay) {
+    aa::AttendArgs a;
+    a.q = view(p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n);
+    a.k = view(p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n);
+    a.v = view(p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n);
+    a.out = static_cast<__nv_bfloat16*>(p->out);
+    a.osb = p->o_stride_b;
+    a.osh = p->o_stride_h;
+    a.osn = p->o_stride_n;
+    a.M = ws_ptr<float>(p, lay.m_off);
+    a.L = ws_ptr<float>(p, lay.l_off);
+    a.Acc = ws_ptr<float>(p, lay.acc_off);
+    a.counts = ws_ptr<int32_t>(p, lay.counts_off);
+    a.ids = ws_ptr<int32_t>(p, lay.ids_off);
+    a.ids_per_head = lay.ids_per_head;
+    a.B = p->B;
+    a.H = p->H;
+    a.Hkv = p->Hkv;
+    a.N = p->N;
+    a.step = p->step;
+    a.sm_scale = (float)scale_of(p);
+    return a;
+}
+
+int clear_status(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
+    cudaError_t e = cudaMemsetAsync(ws_ptr<int32_t>(p, lay.status_off), 0, 4 * sizeof(int32_t), st);
+    return e == cudaSuccess ? AA_OK : cuda_fail(e, "cudaMemsetAsync(status)");
+}
+
+template <int MODE>
+int launch_attend(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
+    static thread_local int configured_dev[2] = {-1, -1};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (configured_dev[MODE] != dev) {
+        e = cudaFuncSetAttribute(aa::attend_mma_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 aa::kAttendSmem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend)");
+        configured_dev[MODE] = dev;
+    }
+    const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / aa::kQRows));
+    aa::attend_mma_kernel<MODE><<<grid, aa::kAttendThreads, aa::kAttendSmem, st>>>(attend_args(p, lay));
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1" : "launch step3");
+    return AA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t aa_id_row_offset(int32_t block_size, int32_t step, int32_t b) {
+    if (b <= 0) return 0;
+    const int64_t G = (int64_t)block_size * step;
+    return G * b * (b - 1) / 2 - 2 * (int64_t)block_size * (b - 1);
+}
+
+int aa_workspace_layout(const aa_params_t* p, aa_workspace_layout_t* lay) {
+    if (!lay) return AA_ERR_NULL;
+    int rc = check_shape(p);
+    if (rc) return rc;
+    const size_t B = p->B, H = p->H, N = p->N, D = p->D;
+    const size_t NB = N / ((size_t)p->block_size * p->step);
+    const size_t BH = B * H;
+    lay->ids_per_head = aa_id_row_offset(p->block_size, p->step, (int32_t)NB);
+    size_t off = 0;
+    lay->m_off = off;       off = align_up(off + BH * N * sizeof(float));
+    lay->l_off = off;       off = align_up(off + BH * N * sizeof(float));
+    lay->acc_off = off;     off = align_up(off + BH * N * D * sizeof(float));
+    lay->qpool_off = off;   off = align_up(off + BH * (N / p->block_size) * D * 2);
+    lay->apool_off = off;   off = align_up(off + BH * (N / p->block_size) * sizeof(float));
+    lay->bitmap_off = off;  off = align_up(off + BH * NB * (N / 32) * sizeof(uint32_t));
+    lay->counts_off = off;  off = align_up(off + BH * NB * sizeof(int32_t));
+    lay->ids_off = off;     off = align_up(off + BH * (size_t)lay->ids_per_head * sizeof(int32_t) + 256);
+    lay->status_off = off;  off = align_up(off + 4 * sizeof(int32_t));
+    lay->total_bytes = off;
+    return AA_OK;
+}
+
+int aa_workspace_bytes(const aa_params_t* p, size_t* bytes) {
+    if (!bytes) return AA_ERR_NULL;
+    aa_workspace_layout_t lay;
+    int rc = aa_workspace_layout(p, &lay);
+    if (rc) return rc;
+    *bytes = lay.total_bytes;
+    return AA_OK;
+}
+
+int aa_step1_anchor(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    rc = clear_status(p, lay, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    return launch_attend<aa::kWindow>(p, lay, static_cast<cudaStream_t>(stream));
+}
+
+int aa_step2_stripes(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int NB = p->N / (p->block_size * p->step);
+    const int Hg = p->H / p->Hkv;
+    const double sm = scale_of(p);
+    // the reference forms both constants in double precision on the host and passes
+    // them to the kernel as fp32 (anchor_attn_v4.py:298, get_mask_test.py:86)
+    const float qk_scale = (float)(sm * 1.44269504);
+    const float diff = (float)(p->theta * 1.44269504);
+
+    __nv_bfloat16* qpool = ws_ptr<__nv_bfloat16>(p, lay.qpool_off);
+    float* apool = ws_ptr<float>(p, lay.apool_off);
+    uint32_t* bitmap = ws_ptr<uint32_t>(p, lay.bitmap_off);
+    int32_t* counts = ws_ptr<int32_t>(p, lay.counts_off);
+    int32_t* ids = ws_ptr<int32_t>(p, lay.ids_off);
+
+    aa::pool_kernel<<<dim3(p->N / 128, p->H, p->B), 64, 0, st>>>(
+        view(p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n), ws_ptr<float>(p, lay.m_off), qpool, apool, p->H,
+        p->N);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch pool");
+
+    if (NB > 1) {
+        const size_t smem = (size_t)Hg * p->step * aa::kRowBytes + 2 * 128 * aa::kRowBytes;
+        if (smem > 227 * 1024) return AA_ERR_TOO_LARGE;
+        static thread_local int configured_dev = -1;
+        static thread_local size_t configured_smem = 0;
+        int dev = 0;
+        e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+        if (configured_dev != dev || configured_smem < smem) {
+            e = cudaFuncSetAttribute(aa::score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(score)");
+            configured_dev = dev;
+            configured_smem = smem;
+        }
+        const int max_tiles = (NB - 1) * p->step - 2;
+        dim3 grid((max_tiles + aa::kTilesPerCta - 1) / aa::kTilesPerCta, NB - 1, p->B * p->Hkv);
+        aa::score_kernel<<<grid, 128, smem, st>>>(view(p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n), qpool,
+                                                  apool, bitmap, p->H, p->Hkv, p->N, p->step, qk_scale, diff);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "launch score");
+    }
+    aa::compact_kernel<<<dim3(NB, p->H, p->B), 256, 0, st>>>(bitmap, ids, counts, p->H, p->N, p->step,
+                                                            lay.ids_per_head);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch compact");
+    return AA_OK;
+}
+
+int aa_step3_sparse(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    return launch_attend<aa::kStripe>(p, lay, static_cast<cudaStream_t>(stream));
+}
+
+int aa_forward(const aa_params_t* p, void* stream) {
+    int rc = aa_step1_anchor(p, stream);
+    if (rc) return rc;
+    rc = aa_step2_stripes(p, stream);
+    if (rc) return rc;
+    return aa_step3_sparse(p, stream);
+}
+
+int aa_check_status(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    int32_t status[4] = {0, 0, 0, 0};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(status, ws_ptr<int32_t>(p, lay.status_off), sizeof(status),
+                                    cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return status[0] == 0 ? AA_OK : AA_ERR_DEVICE_TIMEOUT;
+}
+
+int aa_total_selected(const aa_params_t* p, void* stream, int64_t* total) {
+    if (!total) return AA_ERR_NULL;
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    const size_t n = (size_t)p->B * p->H * (p->N / (p->block_size * p->step));
+    int32_t* host = (int32_t*)malloc(n * sizeof(int32_t));
+    if (!host) return AA_ERR_TOO_LARGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(host, ws_ptr<int32_t>(p, lay.counts_off), n * sizeof(int32_t),
+                                    cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        free(host);
+        return cuda_fail(e, "read counts");
+    }
+    int64_t s = 0;
+    for (size_t i = 0; i < n; ++i) s += host[i];
+    free(host);
+    *total = s;
+    return AA_OK;
+}
+
+const char* aa_strerror(int code) {
+    switch (code) {
+        case AA_OK: return "ok";
+        case AA_ERR_NULL: return "a required pointer is NULL";
+        case AA_ERR_SHAPE: return "bad shape: B, H, Hkv, N must be positive and Hkv must divide H";
+        case AA_ERR_HEAD_DIM: return "head dimension must be 128";
+        case AA_ERR_STEP: return "Invalid step size. Only step sizes 16 or 32 are supported.";
+        case AA_ERR_BLOCK: return "block_size must be 128";
+        case AA_ERR_SEQ: return "Sequence length must be divisible by (block_size * step)";
+        case AA_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
+        case AA_ERR_STRIDE: return "pointers must be 16-byte aligned and strides multiples of 8 elements";
+        case AA_ERR_DTYPE: return "only bf16 is supported";
+        case AA_ERR_CUDA: return "CUDA call failed";
+        case AA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        case AA_ERR_TOO_LARGE: return "problem too large for this entry point";
+        default: return "unknown error";
+    }
+}
+
+const char* aa_last_cuda_error(void) { return g_cuda_err; }
+int aa_version(void) { return 1; }
+int aa_launches_per_forward(void) { return 5; }
+
+}  // extern "C"

@@ -1,0 +1,207 @@
+"""Host side of the operator: the reference's ``anchor_attn`` entry point backed by
+the CUDA library through its C ABI.
+
+Mirrors ``anchor_attn`` of the reference (anchor_attn/src/ops/anchor_attn_v4.py:291-324):
+same name, positional/keyword signature, defaults, assertions and return
+convention.  In addition K and V may carry fewer heads than Q (grouped-query
+attention); query head h then reads KV head ``h // (H // Hkv)``, which is what
+the reference's caller obtains by expanding K/V with ``repeat_kv`` first
+(anchor_attn/src/modules/llama/anchor_attention.py:89-91).
+
+PyTorch is used for device memory and the current stream only.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+__all__ = ["anchor_attn", "AnchorAttnCall", "launches_per_forward"]
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tensor:
+    """One scratch buffer per (device, stream), grown on demand and reused."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_id)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        _workspaces.pop(key, None)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _usable(t: torch.Tensor) -> torch.Tensor:
+    """The kernels take any [B,h,N,D] view whose D axis is contiguous and whose
+    other strides and base address are 16-byte multiples; anything else is copied."""
+    ok = t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+class AnchorAttnCall:
+    """One prepared operator call: validated shapes, the parameter block and
+    typed views of the workspace.  ``run()`` enqueues the whole operator;
+    ``step1()``, ``step2()``, ``step3()`` enqueue one step each (used by tests to
+    look at the intermediate state)."""
+
+    def __init__(self, Q, K, V, sm_scale=None, block_size=128, step=16, difference=12.0,
+                 out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None):
+        lib = _lib.load()
+        assert Q.dim() == 4 and K.dim() == 4 and V.dim() == 4, "Q, K, V must be [B, H, N, D]"
+        assert Q.is_cuda and K.is_cuda and V.is_cuda, "Q, K, V must be CUDA tensors (there is no CPU path)"
+        assert Q.dtype == torch.bfloat16 and K.dtype == Q.dtype and V.dtype == Q.dtype, \
+            "Q, K, V must be bfloat16"
+        assert step in [16, 32], \
+            f"Invalid step size: {step}. Only step sizes 16 or 32 are supported."
+        assert block_size == 128, f"block_size {block_size} is not supported (128 only)"
+        assert Q.size(-2) % (block_size * step) == 0, \
+            f"Sequence length {Q.size(-2)} must be divisible by (block_size * step = {block_size * step})."
+        B, H, N, D = Q.shape
+        Hkv = K.shape[1]
+        assert D == 128, f"head dimension {D} is not supported (128 only)"
+        assert K.shape == V.shape and K.shape[0] == B and K.shape[2] == N and K.shape[3] == D, \
+            "K and V must be [B, Hkv, N, D] with the batch, length and head size of Q"
+        assert H % Hkv == 0, f"{Hkv} KV heads do not divide {H} query heads"
+        self.Q, self.K, self.V = _usable(Q), _usable(K), _usable(V)
+        self.out = out if out is not None else torch.empty((B, H, N, D), dtype=Q.dtype, device=Q.device)
+        self.B, self.H, self.Hkv, self.N, self.D = B, H, Hkv, N, D
+        self.block_size, self.step = block_size, step
+        self.NB = N // (block_size * step)
+        p = _lib.AAParams()
+        p.B, p.H, p.Hkv, p.N, p.D = B, H, Hkv, N, D
+        p.block_size, p.step, p.dtype = block_size, step, _lib.AA_BF16
+        p.theta = float(difference)
+        p.sm_scale = float(sm_scale) if sm_scale else 0.0
+        p.q, p.k, p.v, p.out = self.Q.data_ptr(), self.K.data_ptr(), self.V.data_ptr(), self.out.data_ptr()
+        for name, t in (("q", self.Q), ("k", self.K), ("v", self.V), ("o", self.out)):
+            setattr(p, f"{name}_stride_b", t.stride(0))
+            setattr(p, f"{name}_stride_h", t.stride(1))
+            setattr(p, f"{name}_stride_n", t.stride(2))
+        lay = _lib.AALayout()
+        rc = lib.aa_workspace_layout(ctypes.byref(p), ctypes.byref(lay))
+        if rc != _lib.AA_OK:
+            raise AssertionError(_lib.error_text(rc))
+        self.layout = lay
+        self.stream = torch.cuda.current_stream(Q.device)
+        if workspace is None:
+            workspace = _workspace(Q.device, self.stream.cuda_stream, lay.total_bytes)
+        self.workspace = workspace
+        p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel()
+        self.params = p
+        self._lib = lib
+
+    # ---- launches -------------------------------------------------------
+    def _call(self, fn):
+        with torch.cuda.device(self.Q.device):
+            rc = fn(ctypes.byref(self.params), ctypes.c_void_p(self.stream.cuda_stream))
+        if rc != _lib.AA_OK:
+            raise RuntimeError(f"anchor_attn: {_lib.error_text(rc)}")
+
+    def run(self):
+        self._call(self._lib.aa_forward)
+        return self.out
+
+    def step1(self):
+        self._call(self._lib.aa_step1_anchor)
+
+    def step2(self):
+        self._call(self._lib.aa_step2_stripes)
+
+    def step3(self):
+        self._call(self._lib.aa_step3_sparse)
+        return self.out
+
+    def check_status(self):
+        self._call(self._lib.aa_check_status)
+
+    # ---- typed views of the workspace ----------------------------------
+    def _view(self, off, count, dtype):
+        size = torch.empty((), dtype=dtype).element_size()
+        return self.workspace[off: off + count * size].view(dtype)
+
+    @property
+    def M(self):
+        return self._view(self.layout.m_off, self.B * self.H * self.N, torch.float32).view(self.B, self.H, self.N)
+
+    @property
+    def L(self):
+        return self._view(self.layout.l_off, self.B * self.H * self.N, torch.float32).view(self.B, self.H, self.N)
+
+    @property
+    def Acc(self):
+        return self._view(self.layout.acc_off, self.B * self.H * self.N * self.D, torch.float32).view(
+            self.B, self.H, self.N, self.D)
+
+    @property
+    def qpool(self):
+        n = self.N // self.block_size
+        return self._view(self.layout.qpool_off, self.B * self.H * n * self.D, torch.bfloat16).view(
+            self.B, self.H, n, self.D)
+
+    @property
+    def apool(self):
+        n = self.N // self.block_size
+        return self._view(self.layout.apool_off, self.B * self.H * n, torch.float32).view(self.B, self.H, n)
+
+    @property
+    def counts(self):
+        return self._view(self.layout.counts_off, self.B * self.H * self.NB, torch.int32).view(
+            self.B, self.H, self.NB)
+
+    @property
+    def ids(self):
+        return self._view(self.layout.ids_off, self.B * self.H * self.layout.ids_per_head, torch.int32).view(
+            self.B, self.H, self.layout.ids_per_head)
+
+    def id_row_offset(self, b: int) -> int:
+        return self._lib.aa_id_row_offset(self.block_size, self.step, b)
+
+    def id_lists(self) -> List[List[List[torch.Tensor]]]:
+        """[B][H][NB] ascending int32 id tensors on the CPU (synchronises)."""
+        counts = self.counts.cpu()
+        ids = self.ids.cpu()
+        return [[[ids[z, h, self.id_row_offset(b): self.id_row_offset(b) + int(counts[z, h, b])].clone()
+                  for b in range(self.NB)] for h in range(self.H)] for z in range(self.B)]
+
+    def coords_reference_layout(self):
+        """(true_coords [B,H,NB,N], true_counts [B,H,NB,1]) as the reference's
+        step 2 returns them (get_mask_test.py:138-145); slots past the count are 0."""
+        coords = torch.zeros((self.B, self.H, self.NB, self.N), dtype=torch.int32, device=self.Q.device)
+        counts = self.counts
+        for b in range(1, self.NB):
+            cap = b * self.block_size * self.step - 2 * self.block_size
+            off = self.id_row_offset(b)
+            seg = self.ids[:, :, off: off + cap]
+            keep = torch.arange(cap, device=seg.device)[None, None, :] < counts[:, :, b: b + 1]
+            coords[:, :, b, :cap] = torch.where(keep, seg, torch.zeros_like(seg))
+        return coords, counts.unsqueeze(-1).clone()
+
+    def ratio(self) -> torch.Tensor:
+        """anchor_attn_v4.py:271."""
+        denom = (self.B * self.H * self.N * self.N / (self.block_size * self.step)) // 2
+        return self.counts.sum() / denom
+
+
+def anchor_attn(Q, K, V,
+                sm_scale: float = None,
+                block_size: int = 128,
+                step: int = 16,
+                difference: float = 12,
+                return_computational_ratio: bool = True):
+    """Anchor attention prefill.  Q [B,H,N,D]; K, V [B,H,N,D] or [B,Hkv,N,D]; bf16.
+    Returns ``(out, ratio)`` or ``out`` exactly like the reference operator
+    (anchor_attn/src/ops/anchor_attn_v4.py:291-324); ``out`` is a new [B,H,N,D]
+    tensor.  The launches are asynchronous on the current CUDA stream."""
+    call = AnchorAttnCall(Q, K, V, sm_scale, block_size, step, difference)
+    out = call.run()
+    if return_computational_ratio:
+        return out, call.ratio()
+    return out
+
+
+def launches_per_forward() -> int:
+    return _lib.load().aa_launches_per_forward()

@@ -56,9 +56,10 @@ typedef struct aa_params {
     int32_t block_size;        /* 128 (patch.py:36-40 "block_size_M")                    */
     int32_t step;              /* 16 or 32 (patch.py:36-40 "step")                       */
     int32_t dtype;             /* AA_BF16                                                */
-    float   theta;             /* "difference"/theta in natural-log units, default 12;
+    double  theta;             /* "difference"/theta in natural-log units, default 12;
                                   the library multiplies by log2(e) as anchor_attn_v4.py:298 does */
-    float   sm_scale;          /* 0 => D^-0.5 (anchor_attn_v4.py:312)                    */
+    double  sm_scale;          /* 0 => D^-0.5 (anchor_attn_v4.py:312); a double because the
+                                  reference derives its fp32/bf16 constants from a Python float */
     const void *q, *k, *v;     /* device pointers, bf16                                  */
     void       *out;           /* device pointer, bf16, same logical shape as q          */
     int64_t q_stride_b, q_stride_h, q_stride_n;

@@ -75,13 +75,14 @@ def scale_q_step3(q: torch.Tensor, sm_scale: float, mode: str) -> torch.Tensor:
 # --------------------------------------------------------------------------
 # step 1
 # --------------------------------------------------------------------------
-def step1(q, k, v, sm_scale, block_size=128, step=16, mode="bf16"):
+def step1(q, k, v, sm_scale, block_size=128, step=16, mode="bf16", blocks=None):
     """Window attention over the first ``block_size*step`` keys plus the query's
     own big block, causal.  q [N,D] of one head; k, v [N,D] of its KV head.
     Returns (M [N], L [N], Acc [N,D]) fp32, M in the log2 domain.
     Follows anchor_step_1_2_v2.py:119-161 (tile-by-tile online softmax with an
     additive -1e6 mask); tiles that are masked out entirely leave the running
-    state unchanged bit for bit and are skipped."""
+    state unchanged bit for bit and are skipped.  ``blocks`` restricts the work
+    to the query rows of those big blocks (other rows are left at NaN)."""
     rd = _rounder(mode)
     N, D = q.shape
     T = 128  # BLOCK_SZ_M == BLOCK_SZ_N in the reference's launch (anchor_attn_v4.py:232)
@@ -89,13 +90,15 @@ def step1(q, k, v, sm_scale, block_size=128, step=16, mode="bf16"):
     qs = scale_q_step1(q, sm_scale, mode)
     kf = k.to(torch.float32)
     vf = v.to(torch.float32)
-    M = torch.empty(N, dtype=torch.float32)
-    L = torch.empty(N, dtype=torch.float32)
-    Acc = torch.empty(N, D, dtype=torch.float32)
+    M = torch.full((N,), float("nan"), dtype=torch.float32)
+    L = torch.full((N,), float("nan"), dtype=torch.float32)
+    Acc = torch.full((N, D), float("nan"), dtype=torch.float32)
     ar = torch.arange(T)
     for qb in range(N // T):
         rows = slice(qb * T, (qb + 1) * T)
         b = (qb * T) // G
+        if blocks is not None and b not in blocks:
+            continue
         init_end = min(G, (qb + 1) * T)
         local_start = max(b * G, init_end)
         tiles = list(range(0, init_end, T)) + list(range(local_start, (qb + 1) * T, T))
@@ -173,7 +176,7 @@ def pool_anchor(M: torch.Tensor, block_size: int, mode: str, order: str = "tree"
 
 
 def step2(q, k, M, sm_scale, theta, block_size=128, step=16, mode="bf16", order="tree",
-          return_margin: bool = False, diff_add: str = "fp32"):
+          return_margin: bool = False, diff_add: str = "fp32", blocks=None):
     """Difference-aware stripe identification for one head.
     Returns a list (one entry per big block) of ascending int32 column ids.
     Follows get_mask_test.py:86-124: candidates of big block b are the columns
@@ -203,7 +206,7 @@ def step2(q, k, M, sm_scale, theta, block_size=128, step=16, mode="bf16", order=
     margins = []
     for b in range(NB):
         lo, hi = block_size, b * G - block_size
-        if hi <= lo:
+        if hi <= lo or (blocks is not None and b not in blocks):
             ids.append(torch.empty(0, dtype=torch.int32))
             margins.append(None)
             continue
@@ -245,7 +248,7 @@ def step2_dense_check(q, k, M, sm_scale, theta, block_size=128, step=16):
 # --------------------------------------------------------------------------
 # step 3
 # --------------------------------------------------------------------------
-def step3(q, k, v, ids, M, L, Acc, sm_scale, block_size=128, step=16, mode="bf16"):
+def step3(q, k, v, ids, M, L, Acc, sm_scale, block_size=128, step=16, mode="bf16", blocks=None):
     """Continue the online softmax of step 1 over the selected columns, 128 ids
     at a time (anchor_attn_v4.py:62-105).  The 16 query blocks of a big block
     share one id list, so they are processed together; per-row arithmetic is
@@ -256,8 +259,10 @@ def step3(q, k, v, ids, M, L, Acc, sm_scale, block_size=128, step=16, mode="bf16
     qs = scale_q_step3(q, sm_scale, mode)
     kf = k.to(torch.float32)
     vf = v.to(torch.float32)
-    out = torch.empty(N, D, dtype=torch.float32)
+    out = torch.full((N, D), float("nan"), dtype=torch.float32)
     for b in range(N // G):
+        if blocks is not None and b not in blocks:
+            continue
         rows = slice(b * G, (b + 1) * G)
         m_i, l_i, acc = M[rows].clone(), L[rows].clone(), Acc[rows].clone()
         idb = ids[b].long()
@@ -325,6 +330,20 @@ def anchor_attn_oracle(Q, K, V, sm_scale=None, block_size=128, step=16, differen
         all_ids.append(ids_z)
     ratio = float(counts.sum()) / ((B * H * N * N / (block_size * step)) // 2)   # anchor_attn_v4.py:271
     return OracleResult(out, all_ids, counts, Ms, Ls, Accs, ratio)
+
+
+def oracle_big_blocks(q, k, v, blocks, sm_scale=None, block_size=128, step=16, difference=12.0,
+                      mode="bf16", order="tree"):
+    """Everything the operator computes for the query rows of the given big
+    blocks of ONE head (q [N,D]; k, v [N,D] of its KV head): used to check
+    full-size problems on a sample of blocks.  Returns (M, L, Acc, ids, out) with
+    rows outside ``blocks`` left at NaN / empty."""
+    D = q.shape[-1]
+    sm_scale = sm_scale if sm_scale else 1.0 / (D ** 0.5)
+    M, L, Acc = step1(q, k, v, sm_scale, block_size, step, mode, blocks=blocks)
+    ids = step2(q, k, torch.nan_to_num(M), sm_scale, difference, block_size, step, mode, order, blocks=blocks)
+    out = step3(q, k, v, ids, M, L, Acc, sm_scale, block_size, step, mode, blocks=blocks)
+    return M, L, Acc, ids, out
 
 
 def dense_causal_attention(Q, K, V, sm_scale=None) -> torch.Tensor:

@@ -1,0 +1,98 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header
+declares, and its host-only entry points (layout, validation, error text) behave."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from anchor_attention_b200 import _lib
+
+HEADER = os.path.join(os.path.dirname(__file__), "..", "include", "anchor_attn_b200.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(aa_[a-z0-9_]+)\s*\(", text)))
+
+
+def _params(N=8192, H=4, Hkv=1, step=16, block=128, D=128):
+    p = _lib.AAParams()
+    p.B, p.H, p.Hkv, p.N, p.D = 1, H, Hkv, N, D
+    p.block_size, p.step, p.dtype = block, step, _lib.AA_BF16
+    p.theta = 12.0
+    return p
+
+
+def test_exports_every_declared_symbol(lib):
+    declared = _declared_symbols()
+    assert len(declared) >= 13
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert sorted(_lib.EXPORTS) == sorted(n for n in declared if n not in ("aa_params_t",))
+
+
+def test_id_row_offsets(lib):
+    # capacity of big block b is b*G - 256
+    off = 0
+    for b in range(0, 70):
+        assert lib.aa_id_row_offset(128, 16, b) == off
+        off += max(0, b * 2048 - 256)
+    off = 0
+    for b in range(0, 20):
+        assert lib.aa_id_row_offset(128, 32, b) == off
+        off += max(0, b * 4096 - 256)
+
+
+def test_workspace_layout(lib):
+    p = _params(N=131072, H=32, Hkv=8)
+    lay = _lib.AALayout()
+    assert lib.aa_workspace_layout(ctypes.byref(p), ctypes.byref(lay)) == 0
+    n = ctypes.c_size_t()
+    assert lib.aa_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    assert n.value == lay.total_bytes
+    offs = [lay.m_off, lay.l_off, lay.acc_off, lay.qpool_off, lay.apool_off, lay.bitmap_off, lay.counts_off,
+            lay.ids_off, lay.status_off, lay.total_bytes]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert lay.l_off - lay.m_off >= 32 * 131072 * 4
+    assert lay.qpool_off - lay.acc_off >= 32 * 131072 * 128 * 4
+    assert lay.ids_per_head == sum(b * 2048 - 256 for b in range(1, 64))
+    assert lay.status_off - lay.ids_off >= 32 * lay.ids_per_head * 4
+    assert lay.total_bytes < 4 * 2 ** 30       # a few GB at the largest benchmark shape
+
+
+@pytest.mark.parametrize("change,code", [
+    (dict(D=64), -3), (dict(step=8), -4), (dict(block=64), -5), (dict(N=3000), -6),
+    (dict(H=3, Hkv=2), -2), (dict(N=0), -2),
+])
+def test_shape_validation(lib, change, code):
+    p = _params(**change)
+    n = ctypes.c_size_t()
+    assert lib.aa_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == code
+    assert len(lib.aa_strerror(code)) > 3
+
+
+def test_forward_rejects_null_and_misaligned_before_touching_cuda(lib):
+    p = _params()
+    assert lib.aa_forward(ctypes.byref(p), None) == -1                 # NULL q/k/v/out
+    p.q = p.k = p.v = p.out = 4096
+    p.q_stride_n = 130                                                 # not a multiple of 8 elements
+    assert lib.aa_forward(ctypes.byref(p), None) == -8
+    p.q_stride_n = 128
+    assert lib.aa_forward(ctypes.byref(p), None) == -7                 # no workspace
+    assert lib.aa_forward(None, None) == -1
+
+
+def test_error_text_mirrors_reference_messages(lib):
+    assert b"Only step sizes 16 or 32 are supported" in lib.aa_strerror(-4)
+    assert b"divisible by (block_size * step)" in lib.aa_strerror(-6)
+    assert lib.aa_version() >= 1 and lib.aa_launches_per_forward() >= 3
+
+
+def test_python_entry_point_refuses_cpu_tensors(lib):
+    import torch
+    from anchor_attention_b200 import anchor_attn
+    q = torch.zeros(1, 1, 2048, 128, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="no CPU path"):
+        anchor_attn(q, q, q)
