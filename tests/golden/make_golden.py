@@ -46,6 +46,8 @@ def main():
     ap.add_argument("--cases", default="")
     ap.add_argument("--workdir", default="/tmp/anchor_golden_work")
     args = ap.parse_args()
+    args.out = os.path.abspath(args.out)
+    args.ref_root = os.path.abspath(args.ref_root)
 
     import torch
     gpu = torch.cuda.is_available()
