@@ -8,7 +8,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include "attend_mma.cuh"
+#include "attend_tc.cuh"
 #include "common.cuh"
 #include "stripe.cuh"
 
@@ -93,23 +93,105 @@ int clear_status(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStr
     return e == cudaSuccess ? AA_OK : cuda_fail(e, "cudaMemsetAsync(status)");
 }
 
+// ---- tensor maps for the TMA tile loads of K and V ----------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// A [B, heads, N, 128] bf16 tensor with arbitrary (16-byte multiple) strides as a 4-D
+// tensor map: dimension 0 is the head dimension, the other three are ordered by
+// increasing stride; pos_* tell the kernel which coordinate carries n / head / batch.
+// Box: 64 elements x 128 rows, 128-byte swizzle.
+int make_kv_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, int64_t sn, int B, int heads, int N,
+                int* pos_n, int* pos_h, int* pos_b) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+        return AA_ERR_CUDA;
+    }
+    struct Dim { int64_t stride; uint64_t size; int which; };   // which: 0 = n, 1 = head, 2 = batch
+    Dim d[3] = {{sn, (uint64_t)N, 0}, {sh, (uint64_t)heads, 1}, {sb, (uint64_t)B, 2}};
+    // size-1 dimensions go last (their stride is irrelevant); otherwise sort by stride
+    for (int i = 0; i < 3; ++i)
+        for (int j = i + 1; j < 3; ++j) {
+            const bool swap = (d[i].size == 1 && d[j].size != 1) ||
+                              (!(d[j].size == 1 && d[i].size != 1) && d[j].stride < d[i].stride);
+            if (swap) { Dim t = d[i]; d[i] = d[j]; d[j] = t; }
+        }
+    cuuint64_t gdim[4] = {128, d[0].size, d[1].size, d[2].size};
+    cuuint64_t gstr[3];
+    for (int i = 0; i < 3; ++i) {
+        int64_t st = d[i].stride;
+        if (d[i].size == 1) st = (i == 0) ? 128 : (int64_t)(gstr[i - 1] / 2 * gdim[i]);   // any legal value
+        gstr[i] = (cuuint64_t)st * 2;
+    }
+    cuuint32_t box[4] = {64, 128, 1, 1};
+    if (d[0].which != 0) {
+        // the row dimension is not the innermost of the three: boxes still span 128 rows
+        box[1] = 1;
+        for (int i = 0; i < 3; ++i)
+            if (d[i].which == 0) box[1 + i] = 128;
+    }
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return AA_ERR_CUDA;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (d[i].which == 0) *pos_n = i;
+        if (d[i].which == 1) *pos_h = i;
+        if (d[i].which == 2) *pos_b = i;
+    }
+    return AA_OK;
+}
+
 template <int MODE>
-int launch_attend(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
+int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
     static thread_local int configured_dev[2] = {-1, -1};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     if (configured_dev[MODE] != dev) {
-        e = cudaFuncSetAttribute(aa::attend_mma_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 aa::kAttendSmem);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend)");
+        e = cudaFuncSetAttribute(aa::tc::attend_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 aa::tc::kSmemTotal);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend_tc)");
         configured_dev[MODE] = dev;
     }
-    const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / aa::kQRows));
-    aa::attend_mma_kernel<MODE><<<grid, aa::kAttendThreads, aa::kAttendSmem, st>>>(attend_args(p, lay));
+    aa::tc::TcArgs ta;
+    ta.a = attend_args(p, lay);
+    ta.status = ws_ptr<int32_t>(p, lay.status_off);
+    CUtensorMap kmap, vmap;
+    int rc = make_kv_map(&kmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.kpos_n,
+                         &ta.kpos_h, &ta.kpos_b);
+    if (rc) return rc;
+    rc = make_kv_map(&vmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.vpos_n,
+                     &ta.vpos_h, &ta.vpos_b);
+    if (rc) return rc;
+    const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / (2 * aa::tc::kTile)));
+    aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, ta);
     e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1" : "launch step3");
+    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)" : "launch step3 (tc)");
     return AA_OK;
+}
+
+template <int MODE>
+int launch_attend(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
+    return launch_attend_tc<MODE>(p, lay, st);
 }
 
 }  // namespace

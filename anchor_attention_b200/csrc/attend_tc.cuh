@@ -1,0 +1,472 @@
+// Steps 1 and 3 on the Blackwell tensor cores (tcgen05 + tensor memory + TMA).
+//
+// One CTA owns 256 query rows of one head (two 128-row tiles A and B that lie
+// in the same big block and therefore share their key/value tiles) and walks a
+// list of 128-row key/value tiles:
+//
+//   kWindow  (step 1)  contiguous tiles of [0, min(G, end)) U [max(b*G, that), end),
+//            end = last query row + 1; additive -1e6 causal mask on diagonal tiles;
+//            query scaled with dtype-rounded constants; writes M, L, Acc.
+//            Reference: anchor_attn/src/ops/anchor_step_1_2_v2.py:8-161.
+//   kStripe  (step 3)  tiles of 128 ids from the big block's id list; state starts
+//            from step 1's (M, L, Acc); slots past the count masked to -inf;
+//            writes bf16(acc / l).  Reference: anchor_attn/src/ops/anchor_attn_v4.py:7-105.
+//
+// Warp roles (384 threads):
+//   warps 0-3   softmax of tile A: thread r owns query row r = tensor-memory lane r
+//   warps 4-7   softmax of tile B
+//   warp  8     MMA issuer (one elected lane): S = Q K^T and O += P V with tcgen05.mma
+//   warp  9     loader: TMA box loads for runs of consecutive rows, 16-byte
+//               cp.async row gathers otherwise, into a 5-slot ring of 32 KB tiles
+//   warps 10-11 idle (they only take part in the register re-allocation)
+//
+// Tensor memory (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each.  P (bf16)
+// overwrites the first 64 columns of its S and is consumed from tensor memory as
+// the A operand of the P V product.
+//
+// The running maximum used as the exponent reference is only moved when the
+// true maximum has grown by more than 8 (a factor 256), and the accumulator in
+// tensor memory is rescaled only then; the final scaling makes the result equal
+// to the eager recurrence up to rounding.
+//
+// Every wait is bounded (tc_ptx.cuh); a wait that gives up sets the status word
+// and the CTA drains and frees its tensor memory.
+#pragma once
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace aa {
+namespace tc {
+
+constexpr int kThreads = 384;
+constexpr int kStages = 5;
+constexpr int kTile = 128;                        // rows per query tile and per key tile
+constexpr int kTileBytes = kTile * kRowBytes;     // 32 KB
+constexpr int kSlabBytes = kTileBytes / 2;        // 64 columns x 128 rows, one swizzle slab
+constexpr int kSmemQ = 2 * kTileBytes;
+constexpr int kSmemRing = kStages * kTileBytes;
+constexpr int kSmemBars = 256;
+constexpr int kSmemTotal = kSmemQ + kSmemRing + kSmemBars + 1024;   // + slack to align to 1024
+constexpr float kRescaleThreshold = 8.0f;
+constexpr uint32_t kTmemCols = 512;
+
+struct TcArgs {
+    AttendArgs a;
+    int kpos_n, kpos_h, kpos_b;      // which tensor-map coordinate (1..3 -> 0..2) carries n / head / batch
+    int vpos_n, vpos_h, vpos_b;
+    int32_t* status;
+};
+
+// byte offset of (row, 16-byte chunk) inside a 32 KB tile made of two 128B-swizzled slabs
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
+    return (uint32_t)((chunk >> 3) * kSlabBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int pos_n, int pos_h,
+                                         int pos_b, int row, int head, int z) {
+    const int c0 = pos_n == 0 ? row : (pos_h == 0 ? head : z);
+    const int c1 = pos_n == 1 ? row : (pos_h == 1 ? head : z);
+    const int c2 = pos_n == 2 ? row : (pos_h == 2 ? head : z);
+    tma_load_4d(dst, map, bar, 0, c0, c1, c2);
+    tma_load_4d(dst + kSlabBytes, map, bar, 64, c0, c1, c2);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, TcArgs ta) {
+    extern __shared__ uint8_t smem_raw[];
+    const AttendArgs& a = ta.a;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const uint32_t raw_u = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_u & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t s_u = raw_u + pad;
+    const uint32_t ring_u = s_u + kSmemQ;
+    const uint32_t bars = ring_u + kSmemRing;
+    auto kv_full = [&](int i) { return bars + 8u * i; };
+    auto kv_empty = [&](int i) { return bars + 40u + 8u * i; };
+    auto q_full = [&](int j) { return bars + 80u + 8u * j; };
+    auto s_full = [&](int j) { return bars + 96u + 8u * j; };
+    auto p_ready = [&](int j) { return bars + 112u + 8u * j; };
+    auto o_done = [&](int j) { return bars + 128u + 8u * j; };
+    const uint32_t tmem_slot_u = bars + 144u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemQ + kSmemRing + 144);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 148);
+
+    // ---- which work item ----
+    const int BH = a.B * a.H;
+    const int npairs = a.N / (2 * kTile);
+    const int pair = npairs - 1 - (int)(blockIdx.x / BH);      // heaviest first
+    const int hz = blockIdx.x % BH;
+    const int z = hz / a.H, h = hz % a.H;
+    const int kvh = h / (a.H / a.Hkv);
+    const int G = 128 * a.step;
+    const int b = (pair * 2 * kTile) / G;
+    const int NB = a.N / G;
+
+    int ntiles, n_init = 0, local_start = 0, count = 0;
+    const int32_t* idp = nullptr;
+    if (MODE == kWindow) {
+        const int end = (2 * pair + 2) * kTile;
+        const int init_end = min(G, end);
+        local_start = max(b * G, init_end);
+        n_init = init_end / kTile;
+        ntiles = n_init + (end - local_start) / kTile;
+    } else {
+        count = a.counts[(int64_t)hz * NB + b];
+        ntiles = (count + kTile - 1) / kTile;
+        const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 256 * (int64_t)(b - 1));
+        idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
+    }
+
+    // ---- set-up ----
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(kv_full(i), 32);
+            mbar_init(kv_empty(i), 1);
+        }
+        for (int j = 0; j < 2; ++j) {
+            mbar_init(q_full(j), 128);
+            mbar_init(s_full(j), 1);
+            mbar_init(p_ready(j), 128);
+            mbar_init(o_done(j), 1);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_slot_u, kTmemCols);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // =================================================== softmax warps
+        setmaxnreg_inc<208>();
+        const int j = warp >> 2;
+        const int r = tid & 127;
+        const int qb = 2 * pair + j;
+        const int row_g = qb * kTile + r;
+        const int64_t srow = (int64_t)hz * a.N + row_g;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem_base + lane_base + (uint32_t)j * 128u;
+        const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)j * 128u;
+
+        // Q tile: load, scale, round, store in the K-major 128B-swizzled layout the MMA reads
+        {
+            const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
+            const float c1 = bf16_round(a.sm_scale), c2 = bf16_round(kLog2e);
+            uint8_t* qs = smem + j * kTileBytes;
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+                const int id = r + 128 * i;
+                const int rr = id >> 4, ch = id & 15;
+                uint4 raw = *reinterpret_cast<const uint4*>(qbase + (int64_t)rr * a.q.sn + ch * 8);
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float2 f = __bfloat1622float2(p2[e]);
+                    if (MODE == kWindow) {
+                        f.x = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.x, c1)), c2));
+                        f.y = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.y, c1)), c2));
+                    } else {
+                        f.x = __fmul_rn(__fmul_rn(f.x, a.sm_scale), kLog2e);
+                        f.y = __fmul_rn(__fmul_rn(f.y, a.sm_scale), kLog2e);
+                    }
+                    p2[e] = __floats2bfloat162_rn(f.x, f.y);
+                }
+                *reinterpret_cast<uint4*>(qs + sw_off(rr, ch)) = raw;
+            }
+            fence_proxy_async();
+            mbar_arrive(q_full(j));
+        }
+
+        float m_true, m_ref, l;
+        if (MODE == kStripe) {
+            m_true = m_ref = a.M[srow];
+            l = a.L[srow];
+            if (ntiles > 0) {
+                const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 x = src[c * 8 + i];
+                        v[4 * i] = __float_as_uint(x.x);
+                        v[4 * i + 1] = __float_as_uint(x.y);
+                        v[4 * i + 2] = __float_as_uint(x.z);
+                        v[4 * i + 3] = __float_as_uint(x.w);
+                    }
+                    tmem_st32(tO + c * 32, v);
+                }
+                tmem_wait_st();
+            }
+        } else {
+            m_true = m_ref = -INFINITY;
+            l = 0.f;
+        }
+
+        bool ok = true;
+        for (int t = 0; t < ntiles && ok; ++t) {
+            ok = mbar_wait(s_full(j), t & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t sv[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
+            tmem_wait_ld();
+
+            if (MODE == kWindow) {
+                const int col0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
+                if (col0 + kTile - 1 > qb * kTile) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + c * 32 + i > row_g)
+                                sv[c][i] = __float_as_uint(__uint_as_float(sv[c][i]) + -1e6f);
+                }
+            } else {
+                const int valid = count - t * kTile;
+                if (valid < kTile) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= valid) sv[c][i] = __float_as_uint(-INFINITY);
+                }
+            }
+            {   // row maximum: four independent chains of three-input max
+                float mx[4] = {m_true, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+                m_true = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            }
+            // move the exponent reference only when some row of the warp needs it
+            if (__any_sync(0xffffffffu, m_true > m_ref + kRescaleThreshold)) {
+                const float alpha = fast_exp2(m_ref - m_true);
+                if (!(MODE == kWindow && t == 0)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tO + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st32(tO + c * 32, v);
+                    }
+                }
+                l *= alpha;
+                m_ref = m_true;
+            }
+            float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            const float2 neg_ref = make_float2(-m_ref, -m_ref);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int e = c * 64 + 2 * i;
+                    const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
+                                                            __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
+                    const float2 p = make_float2(fast_exp2(d.x), fast_exp2(d.y));
+                    rs[i & 3] = __fadd2_rn(rs[i & 3], p);
+                    pk[i] = pack_bf16x2(p.x, p.y);
+                }
+                tmem_st32(tS + c * 32, pk);
+            }
+            const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
+            const float rs_total = rsum.x + rsum.y;
+            l += rs_total;
+            tmem_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(p_ready(j));
+        }
+
+        // ---- epilogue ----
+        if (ok && ntiles > 0) {
+            ok = mbar_wait(o_done(j), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            tcgen05_fence_after();
+        }
+        if (ok) {
+            if (MODE == kWindow) {
+                const float sc = fast_exp2(m_ref - m_true);
+                a.M[srow] = m_true;
+                a.L[srow] = l * sc;
+                float4* dst = reinterpret_cast<float4*>(a.Acc + srow * kD);
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tO + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        dst[c * 8 + i] = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
+                                                     __uint_as_float(v[4 * i + 2]) * sc,
+                                                     __uint_as_float(v[4 * i + 3]) * sc);
+                }
+            } else {
+                __nv_bfloat16* orow = a.out + z * a.osb + h * a.osh + (int64_t)row_g * a.osn;
+                const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    if (ntiles > 0) {
+                        tmem_ld32(tO + c * 32, v);
+                        tmem_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 x = src[c * 8 + i];
+                            v[4 * i] = __float_as_uint(x.x);
+                            v[4 * i + 1] = __float_as_uint(x.y);
+                            v[4 * i + 2] = __float_as_uint(x.z);
+                            v[4 * i + 3] = __float_as_uint(x.w);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 o4;
+                        o4.x = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i]), l), __fdiv_rn(__uint_as_float(v[8 * i + 1]), l));
+                        o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
+                        o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
+                        o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o4;
+                    }
+                }
+            }
+        }
+    } else {
+        setmaxnreg_dec<88>();
+        if (warp == 8 && lane == 0 && ntiles > 0) {
+            // =================================================== MMA issuer
+            constexpr uint32_t kIdescQK = idesc_bf16_128x128(0);
+            constexpr uint32_t kIdescPV = idesc_bf16_128x128(1);
+            const uint32_t q_u[2] = {s_u, s_u + (uint32_t)kTileBytes};
+            auto slot_addr = [&](int n) { return ring_u + (uint32_t)(n % kStages) * kTileBytes; };
+            auto issue_qk = [&](int j, uint32_t kaddr) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * kSlabBytes + (ks & 3) * 32);
+                    mma_ss(tmem_base + (uint32_t)j * 128u, smem_desc_sw128(q_u[j] + off, 16),
+                           smem_desc_sw128(kaddr + off, 16), kIdescQK, ks > 0);
+                }
+            };
+            auto issue_pv = [&](int j, uint32_t vaddr, bool acc) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ts(tmem_base + 256u + (uint32_t)j * 128u, tmem_base + (uint32_t)j * 128u + (uint32_t)ks * 8u,
+                           smem_desc_sw128(vaddr + (uint32_t)ks * 2048u, kSlabBytes), kIdescPV, (ks > 0) || acc);
+            };
+            bool ok = mbar_wait(q_full(0), 0, abort_flag) && mbar_wait(q_full(1), 0, abort_flag) &&
+                      mbar_wait(kv_full(0), 0, abort_flag);
+            if (ok) {
+                fence_proxy_async();
+                tcgen05_fence_after();
+                issue_qk(0, slot_addr(0));
+                mma_commit(s_full(0));
+                issue_qk(1, slot_addr(0));
+                mma_commit(s_full(1));
+                mma_commit(kv_empty(0));
+            }
+            for (int t = 0; t < ntiles && ok; ++t) {
+                const int nv = 2 * t + 1, nk = 2 * t + 2;
+                ok = mbar_wait(kv_full(nv % kStages), (nv / kStages) & 1, abort_flag);
+                if (!ok) break;
+                fence_proxy_async();
+                for (int j = 0; j < 2 && ok; ++j) {
+                    ok = mbar_wait(p_ready(j), t & 1, abort_flag);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe));
+                    if (j == 1) mma_commit(kv_empty(nv % kStages));
+                    if (t + 1 < ntiles) {
+                        if (j == 0) {
+                            ok = mbar_wait(kv_full(nk % kStages), (nk / kStages) & 1, abort_flag);
+                            if (!ok) break;
+                            fence_proxy_async();
+                            tcgen05_fence_after();
+                        }
+                        issue_qk(j, slot_addr(nk));
+                        mma_commit(s_full(j));
+                        if (j == 1) mma_commit(kv_empty(nk % kStages));
+                    } else {
+                        mma_commit(o_done(j));
+                    }
+                }
+            }
+        } else if (warp == 9 && ntiles > 0) {
+            // =================================================== loader
+            const __nv_bfloat16* kbase = a.k.ptr + z * a.k.sb + kvh * a.k.sh;
+            const __nv_bfloat16* vbase = a.v.ptr + z * a.v.sb + kvh * a.v.sh;
+            bool ok = true;
+            for (int n = 0; n < 2 * ntiles && ok; ++n) {
+                const int slot = n % kStages, it = n / kStages;
+                if (it > 0) {
+                    ok = mbar_wait(kv_empty(slot), (it - 1) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                const int t = n >> 1;
+                const bool is_v = n & 1;
+                const uint32_t dst = ring_u + (uint32_t)slot * kTileBytes;
+                int row0 = 0;
+                bool run = true;     // 128 consecutive rows -> one TMA tile
+                if (MODE == kWindow) {
+                    row0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
+                } else {
+                    const int s0 = t * kTile;
+                    run = false;
+                    if (s0 + kTile <= count) {
+                        row0 = idp[s0];
+                        run = (idp[s0 + kTile - 1] - row0) == kTile - 1;
+                    }
+                }
+                if (run) {
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(kv_full(slot), kTileBytes);
+                        if (is_v)
+                            tma_tile(dst, &vmap, kv_full(slot), ta.vpos_n, ta.vpos_h, ta.vpos_b, row0, kvh, z);
+                        else
+                            tma_tile(dst, &kmap, kv_full(slot), ta.kpos_n, ta.kpos_h, ta.kpos_b, row0, kvh, z);
+                    } else {
+                        mbar_arrive(kv_full(slot));
+                    }
+                } else {
+                    const __nv_bfloat16* base = is_v ? vbase : kbase;
+                    const int64_t sn = is_v ? a.v.sn : a.k.sn;
+                    const int s0 = t * kTile;
+#pragma unroll 4
+                    for (int i = 0; i < 64; ++i) {
+                        const int id = lane + 32 * i;
+                        const int rr = id >> 4, ch = id & 15;
+                        const bool valid = (s0 + rr) < count;
+                        const int64_t row = valid ? idp[s0 + rr] : 0;
+                        cp_async16(dst + sw_off(rr, ch), base + row * sn + ch * 8, valid ? 16 : 0);
+                    }
+                    cp_async_mbar_arrive_noinc(kv_full(slot));
+                }
+            }
+            cp_async_wait<0>();
+        }
+    }
+
+    // ---- teardown ----
+    tcgen05_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicMax(ta.status, 1);
+    if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+}  // namespace tc
+}  // namespace aa

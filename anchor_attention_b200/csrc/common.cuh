@@ -15,6 +15,25 @@ struct TensorView {          // one [B, heads, N, 128] bf16 tensor, strides in e
     int64_t sb, sh, sn;
 };
 
+// Which of the two attention passes a kernel instance runs.
+enum AttendMode { kWindow = 0, kStripe = 1 };
+
+// Arguments shared by both passes: the tensors, the inter-kernel state in the
+// workspace and the problem sizes.
+struct AttendArgs {
+    TensorView q, k, v;
+    __nv_bfloat16* out;
+    int64_t osb, osh, osn;
+    float* M;
+    float* L;
+    float* Acc;
+    const int32_t* counts;
+    const int32_t* ids;
+    int64_t ids_per_head;
+    int B, H, Hkv, N, step;
+    float sm_scale;
+};
+
 __device__ __forceinline__ float bf16_round(float x) {
     return __bfloat162float(__float2bfloat16_rn(x));
 }
@@ -28,6 +47,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -108,29 +108,36 @@ def measured_peaks():
 # --------------------------------------------------------------------------
 # CPU legs (the only places the oracle is executed by the benchmark)
 # --------------------------------------------------------------------------
-def cpu_sample(N, threads=None):
-    """Time the CPU restatement on a bounded sample of the workload: one query head,
-    the last big block's 2048 query rows, all three steps, then scale by the
-    layer's pair count.  Returns (extrapolated ms per layer, description, cores)."""
+def cpu_sample(N, threads=None, budget_s=12.0):
+    """Time the CPU restatement on a bounded sample of the workload: one query head
+    of the N-token layer, whole big blocks (2048 query rows each, all three steps)
+    taken from the last one downwards until ``budget_s`` seconds are spent, then
+    scaled by the layer's query-key pair count.  Returns (extrapolated ms per
+    layer, description, cores)."""
     import torch
     from oracle.anchor_oracle import oracle_big_blocks, make_inputs
     cores = threads or os.cpu_count()
     torch.set_num_threads(cores)
-    Ns = min(N, 32768)                       # keep the sample to tens of seconds
-    Q, K, V = make_inputs(Ns, 1, 1, seed=0, rope=True)
-    NBs = Ns // (BLOCK * STEP)
-    b = NBs - 1
-    t0 = time.perf_counter()
-    M, L, Acc, ids, out = oracle_big_blocks(Q[0, 0], K[0, 0], V[0, 0], [b], difference=THETA)
-    dt = time.perf_counter() - t0
+    Q, K, V = make_inputs(N, 1, 1, seed=0, rope=True)
     G = BLOCK * STEP
-    sample_pairs = G * G + G * (G + 1) // 2 + G * int(ids[b].numel())
-    cap_total = sum(bb * G - 2 * BLOCK for bb in range(1, N // G))
     NB = N // G
+    oracle_big_blocks(Q[0, 0, :2 * G], K[0, 0, :2 * G], V[0, 0, :2 * G], [1], difference=THETA)   # warm-up
+    sample_pairs, blocks, dt = 0, [], 0.0
+    for b in range(NB - 1, -1, -1):
+        t0 = time.perf_counter()
+        M, L, Acc, ids, out = oracle_big_blocks(Q[0, 0], K[0, 0], V[0, 0], [b], difference=THETA)
+        dt += time.perf_counter() - t0
+        window = G * (G + 1) // 2 + (G * G if b > 0 else 0)
+        sample_pairs += window + G * int(ids[b].numel())
+        blocks.append(b)
+        if dt >= budget_s:
+            break
+    cap_total = sum(bb * G - 2 * BLOCK for bb in range(1, NB))
     layer_pairs = H * (G * (G + 1) // 2 + (NB - 1) * (G * G + G * (G + 1) // 2) + G * cap_total)
     ms = dt * 1e3 * layer_pairs / sample_pairs
-    desc = (f"CPU restatement (torch fp32 matmuls, bf16 rounding points), 1 head, query rows of big block {b} of a "
-            f"{Ns}-token sequence ({sample_pairs / 1e6:.0f} M query-key pairs, {dt:.1f} s), scaled to the layer's "
+    desc = (f"CPU restatement (torch fp32 matmuls, bf16 rounding points) on {cores} threads: 1 head of the "
+            f"{N}-token layer, query rows of big blocks {blocks[0]}..{blocks[-1]} ({len(blocks)} x 2048 rows, "
+            f"{sample_pairs / 1e9:.2f} G query-key pairs, {dt:.1f} s), scaled to the layer's "
             f"{layer_pairs / 1e9:.1f} G pairs at density 1")
     return ms, desc, cores
 

@@ -10,7 +10,8 @@ JIT-compiled and run in bf16 (files ``ref_gpu_bf16_*.npz``).
 The inputs are not stored: they are regenerated from the seed by
 ``oracle.anchor_oracle.make_inputs``; a checksum of the inputs is stored so a
 drift in the generator is detected.  Stored per case: counts, the concatenated
-id lists, M, L, a row subsample of Acc, and the operator output.
+id lists, M, L, a row subsample of Acc, and the operator output (fp16 values for the
+interpreter fixtures, raw bf16 bit patterns as int16 for the GPU fixtures).
 
 The reference functions called are ``anchor_attn_step_1`` / ``anchor_attn_step_2``
 (anchor_attn/src/ops/anchor_step_1_2_v2.py:164-210) and ``anchor_attn``
@@ -92,7 +93,7 @@ def main():
             inputs_sha256=csum, counts=counts, ids=flat,
             M=M.float().cpu().numpy()[0], L=L.float().cpu().numpy()[0],
             Acc_rows16=Acc.float().cpu().numpy()[0, :, ::16],
-            out=out.float().cpu().numpy()[0].astype(np.float16 if not gpu else np.float32),
+            out=(out.view(torch.int16).cpu().numpy()[0] if gpu else out.float().cpu().numpy()[0].astype(np.float16)),
             ratio=float(ratio),
         )
         print(f"{name}: counts sum {counts.sum()} ratio {float(ratio):.4f} in {time.time() - t0:.1f}s", flush=True)

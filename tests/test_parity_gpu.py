@@ -2,8 +2,8 @@
 
 Tolerances.  Index sets: equal to the oracle's up to the documented tie band
 (parity_util.tie_band).  Row maxima M: 2e-3 absolute (fp32 accumulation order
-of a 128-term bf16 dot).  L: 2e-3 relative.  Acc: 2e-2 absolute on values of
-order 1..10.  Output: max abs <= 2e-2 and mean abs <= 1e-3 (the north-star
+of a 128-term bf16 dot).  L: 2e-3 relative.  Acc: 1e-2 of the row's largest
+entry, and 1e-2 absolute after normalising by L.  Output: max abs <= 2e-2 and mean abs <= 1e-3 (the north-star
 tolerance against the reference's own output)."""
 import pytest
 import torch
@@ -41,7 +41,11 @@ def test_full_operator_matches_oracle(lib, N, H, Hkv, theta, rope, q_shift, seed
     M, L, Acc = call.M.cpu(), call.L.cpu(), call.Acc.cpu()
     assert (M - ref.M).abs().max() < 2e-3
     assert ((L - ref.L).abs() / ref.L).max() < 2e-3
-    assert (Acc - ref.Acc).abs().max() < 2e-2
+    # Acc is un-normalised: compare it relative to each row's own magnitude, and the
+    # normalised step-1 output Acc / L absolutely
+    scale = ref.Acc.abs().amax(dim=-1, keepdim=True).clamp_min(1.0)
+    assert ((Acc - ref.Acc).abs() / scale).max() < 1e-2     # both sides round P to bf16 (2^-9 each)
+    assert (Acc / L[..., None] - ref.Acc / ref.L[..., None]).abs().max() < 1e-2
     call.step2()
     ours = call.id_lists()
     counts = call.counts.cpu()
@@ -71,6 +75,44 @@ def test_full_operator_matches_oracle(lib, N, H, Hkv, theta, rope, q_shift, seed
     out2, ratio = anchor_attn(Q.cuda(), K.cuda(), V.cuda(), difference=theta)
     assert torch.equal(out2.cpu(), call.out.cpu())
     assert abs(float(ratio) - float(counts.sum()) / ((H * N * N / 2048) // 2)) < 1e-6
+
+
+GOLDEN_GPU = sorted(__import__("glob").glob(
+    __import__("os").path.join(__import__("os").path.dirname(__file__), "golden", "ref_gpu_bf16_*.npz")))
+
+
+@pytest.mark.parametrize("path", GOLDEN_GPU, ids=[__import__("os").path.basename(p) for p in GOLDEN_GPU])
+def test_against_reference_gpu_fixtures(lib, path):
+    """Our kernels against what the reference's own compiled kernels produced on
+    a B200 (bf16): state of step 1, index sets up to the tie band, final output
+    within the north-star tolerance."""
+    import numpy as np
+    g = np.load(path)
+    N, H, Hkv, theta = int(g["N"]), int(g["H"]), int(g["Hkv"]), float(g["theta"])
+    Q, K, V = make_inputs(N, H, Hkv, seed=int(g["seed"]), rope=bool(g["rope"]), q_shift=float(g["q_shift"]))
+    call = _call(Q, K, V, theta)
+    out = call.run().float().cpu()
+    call.check_status()
+    assert (call.M.cpu()[0] - torch.from_numpy(g["M"])).abs().max() < 1e-4
+    assert ((call.L.cpu()[0] - torch.from_numpy(g["L"])).abs() / torch.from_numpy(g["L"])).max() < 1e-4
+    assert (call.Acc.cpu()[0, :, ::16] - torch.from_numpy(g["Acc_rows16"])).abs().max() < 5e-3
+    ours = call.id_lists()
+    pos = diff = total = 0
+    Mref = torch.from_numpy(g["M"])
+    for h in range(H):
+        for b in range(N // 2048):
+            c = int(g["counts"][h, b])
+            ref_ids = g["ids"][pos:pos + c]
+            pos += c
+            total += c
+            if b:
+                check_id_set(ours[0][h][b], Q[0, h], K[0, h // (H // Hkv)], Mref[h], SM, theta, b)
+            diff += len(set(ref_ids.tolist()) ^ set(ours[0][h][b].tolist()))
+    print(f"\n{__import__('os').path.basename(path)}: {total} selected by the reference, symmetric difference {diff}")
+    assert diff <= max(2, 0.01 * total)
+    out_ref = torch.from_numpy(g["out"]).view(torch.bfloat16).float()
+    err = (out[0] - out_ref).abs()
+    assert err.max() <= OUT_MAX_ABS and err.mean() <= OUT_MEAN_ABS
 
 
 def test_step3_given_oracle_state(lib):
