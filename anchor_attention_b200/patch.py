@@ -1,0 +1,140 @@
+"""Module hook: swap anchor attention into a Hugging Face model's attention forward.
+
+Mirrors ``patch_model(model, pattern, config)`` of the reference
+(anchor_attn/src/modules/patch.py:312-327) for the one pattern this library
+implements, with the reference's configuration keys and defaults
+(``block_size_M=128, theta=12, step=16``, patch.py:36-45) and its handling of
+JSON-string configurations (patch.py:62-74).
+
+The reference binds a new bound-method ``forward`` on every
+``LlamaFlashAttention2`` of transformers 4.45
+(anchor_attn/src/modules/llama/anchor_attention.py:17-117).  Current
+transformers releases route attention through a registry of functions
+``fn(module, query[B,H,N,D], key[B,Hkv,N,D], value, attention_mask, scaling,
+dropout, **kw) -> (out[B,N,H,D], None)``; this module registers one and points
+the model's configuration at it.  The routing rules inside are the reference's
+(anchor_attention.py:72-113):
+
+* prefill (q_len > 1, no earlier cache): the first ``q_len - q_len % (step*block)``
+  tokens go through ``anchor_attn``; the remaining ``pad`` queries attend densely
+  and causally over all keys;
+* decode and chunked prefill: dense causal attention.
+
+One intentional divergence: when ``q_len`` is an exact multiple of
+``step*block`` the reference slices ``x[:, :-0]``, which is empty, and leaves the
+layer's attention output at zero; here ``pad == 0`` means every token goes
+through ``anchor_attn``.
+"""
+from __future__ import annotations
+
+import copy
+import json
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+ATTENTION_CONFIG_EXAMPLE = {
+    "anchor_attn": {"block_size_M": 128, "theta": 12, "step": 16},
+    "anchor_attn_lite": {"block_size_M": 128, "theta": 12, "step": 16},
+}
+ATTN_IMPLEMENTATION_NAME = "anchor_attn"
+MLP_CHUNK = 32768    # tokens per MLP chunk, as anchor_attn/src/modules/llama/llama_mlp_forward.py:49-56
+
+
+def get_config_example(pattern: str = None):
+    if pattern is None:
+        return copy.deepcopy(ATTENTION_CONFIG_EXAMPLE)
+    return copy.deepcopy(ATTENTION_CONFIG_EXAMPLE[pattern])
+
+
+def resolve_config(pattern: str, cfg=None) -> dict:
+    """Defaults merged under the caller's dict or JSON string (patch.py:62-74)."""
+    if pattern not in ATTENTION_CONFIG_EXAMPLE:
+        raise ValueError(f"Unsupported attention pattern {pattern!r}: this library implements "
+                         f"{sorted(ATTENTION_CONFIG_EXAMPLE)} only")
+    if cfg is None:
+        return get_config_example(pattern)
+    if isinstance(cfg, str):
+        try:
+            cfg = json.loads(cfg)
+        except json.JSONDecodeError as e:
+            raise ValueError(f"Configuration string is not valid JSON: {e}")
+    cfg = dict(cfg)
+    for k, v in get_config_example(pattern).items():
+        cfg.setdefault(k, v)
+    return cfg
+
+
+def patch_model_config(model, pattern: str, cfg=None):
+    """Write the hyper-parameters onto ``model.config`` as attributes, where the
+    attention function reads them (patch.py:106-109, anchor_attention.py:74,96-98)."""
+    cfg = resolve_config(pattern, cfg)
+    for k, v in cfg.items():
+        setattr(model.config, k, v)
+    return cfg
+
+
+def _dense_causal(query, key, value, scaling, q_offset):
+    """Dense causal attention of ``query`` (positions q_offset .. q_offset+q-1) over
+    all keys; the comparator path for the tail and for decode (the reference calls
+    flash-attn here, anchor_attention.py:76-88,101-113).  Returns [B,H,q,D]."""
+    q_len, kv_len = query.shape[2], key.shape[2]
+    pos_q = torch.arange(q_offset, q_offset + q_len, device=query.device)[:, None]
+    mask = torch.arange(kv_len, device=query.device)[None, :] <= pos_q
+    return F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling, enable_gqa=True)
+
+
+def anchor_attention_forward(module, query, key, value, attention_mask=None, scaling: Optional[float] = None,
+                             dropout: float = 0.0, anchor_attn_fn=None, **kwargs):
+    """Attention function for the transformers attention registry.
+    query [B,H,N,D]; key, value [B,Hkv,Nk,D]; returns ([B,N,H,D], None)."""
+    if anchor_attn_fn is None:
+        from .ops import anchor_attn as anchor_attn_fn
+    cfg = module.config
+    block, step, theta = int(cfg.block_size_M), int(cfg.step), float(cfg.theta)
+    B, H, q_len, D = query.shape
+    kv_len = key.shape[2]
+    G = block * step
+    out = torch.empty((B, q_len, H, D), dtype=query.dtype, device=query.device)
+    n_sparse = (q_len - q_len % G) if (q_len > 1 and q_len == kv_len) else 0
+    if n_sparse:
+        sparse = anchor_attn_fn(query[:, :, :n_sparse], key[:, :, :n_sparse], value[:, :, :n_sparse],
+                                scaling, block, step, theta, False)
+        out[:, :n_sparse] = sparse.transpose(1, 2)
+    if n_sparse < q_len:
+        tail = _dense_causal(query[:, :, n_sparse:], key, value, scaling, kv_len - (q_len - n_sparse))
+        out[:, n_sparse:] = tail.transpose(1, 2)
+    return out, None
+
+
+def _chunked_mlp_forward(mlp):
+    inner = mlp.forward
+
+    def forward(x):
+        if x.dim() != 3 or x.shape[1] <= MLP_CHUNK:
+            return inner(x)
+        return torch.cat([inner(x[:, i:i + MLP_CHUNK]) for i in range(0, x.shape[1], MLP_CHUNK)], dim=1)
+
+    return forward
+
+
+def patch_model(model, pattern: str, config=None):
+    """Patch a Hugging Face causal LM to use anchor attention for prefill.
+    ``pattern`` must be "anchor_attn" (or its alias "anchor_attn_lite", which the
+    reference maps to the same forward, patch.py:142-144)."""
+    from transformers import AttentionInterface, PreTrainedModel
+    if not isinstance(model, PreTrainedModel):
+        raise ValueError("Only Hugging Face transformers models are supported")
+    name = type(model).__name__.lower()
+    if not any(t in name for t in ("llama", "qwen2", "qwen3", "mistral")):
+        raise ValueError(f"Unsupported model type: {type(model).__name__}")
+    patch_model_config(model, pattern, config)
+    AttentionInterface.register(ATTN_IMPLEMENTATION_NAME, anchor_attention_forward)
+    model.config._attn_implementation = ATTN_IMPLEMENTATION_NAME
+    # memory patch the reference applies with every pattern: the MLP in 32768-token chunks
+    for mod in model.modules():
+        if type(mod).__name__.endswith("MLP") and not getattr(mod, "_anchor_chunked", False):
+            mod.forward = _chunked_mlp_forward(mod)
+            mod._anchor_chunked = True
+    return model

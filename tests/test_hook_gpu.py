@@ -1,0 +1,68 @@
+"""The module hook and the head-parallel wrapper on a B200 (through the C ABI)."""
+import types
+
+import pytest
+import torch
+
+from oracle.anchor_oracle import anchor_attn_oracle, dense_causal_attention, make_inputs
+from parity_util import OUT_MAX_ABS, OUT_MEAN_ABS
+
+pytestmark = pytest.mark.gpu
+
+
+def test_attention_function_prefill_with_tail(lib):
+    from anchor_attention_b200 import patch
+    q_len, H, Hkv = 4096 + 333, 4, 2
+    Q, K, V = make_inputs(8192, H, Hkv, seed=21, rope=True, q_shift=0.5)
+    Q, K, V = Q[:, :, :q_len], K[:, :, :q_len], V[:, :, :q_len]
+    mod = types.SimpleNamespace(config=types.SimpleNamespace(block_size_M=128, step=16, theta=9.5))
+    out, _ = patch.anchor_attention_forward(mod, Q.cuda(), K.cuda(), V.cuda(), None, scaling=128 ** -0.5)
+    out = out.float().cpu().transpose(1, 2)
+    ref = anchor_attn_oracle(Q[:, :, :4096], K[:, :, :4096], V[:, :, :4096], difference=9.5, keep_state=False)
+    err = (out[:, :, :4096] - ref.out).abs()
+    assert err.max() <= OUT_MAX_ABS and err.mean() <= OUT_MEAN_ABS
+    dense = dense_causal_attention(Q, K, V)[:, :, 4096:]
+    assert (out[:, :, 4096:] - dense).abs().max() < 2e-2
+
+
+def test_tiny_llama_prefill_runs_through_the_hook(lib):
+    """A random-init 2-layer Llama-architecture model (head size 128, GQA 4/2):
+    after patch_model the prefill logits equal those of the same model whose
+    attention is the CPU oracle + dense tail (same routing, reference semantics)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from anchor_attention_b200 import patch
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=8192,
+                      rope_theta=500000.0)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+    patch.patch_model(model, "anchor_attn", {"theta": 12})
+    assert model.config._attn_implementation == "anchor_attn" and model.config.step == 16
+    ids = torch.randint(0, 512, (1, 4096 + 50), device="cuda")
+    with torch.no_grad():
+        got = model(ids).logits.float().cpu()
+
+    def oracle_attn(module, query, key, value, attention_mask=None, scaling=None, dropout=0.0, **kw):
+        fn = lambda Q, K, V, s, b, st, th, r: anchor_attn_oracle(      # noqa: E731
+            Q.cpu(), K.cpu(), V.cpu(), s, b, st, th, keep_state=False).out.to(Q.dtype).to(Q.device)
+        return patch.anchor_attention_forward(module, query, key, value, attention_mask, scaling, dropout,
+                                              anchor_attn_fn=fn)
+
+    from transformers import AttentionInterface
+    AttentionInterface.register("anchor_attn_oracle_check", oracle_attn)
+    model.config._attn_implementation = "anchor_attn_oracle_check"
+    with torch.no_grad():
+        want = model(ids).logits.float().cpu()
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < 0.15 and (got - want).abs().mean() < 5e-3
+
+
+def test_head_sharded_wrapper_single_rank(lib):
+    from anchor_attention_b200 import anchor_attn
+    from anchor_attention_b200.parallel import HeadShardedAnchorAttn
+    Q, K, V = make_inputs(4096, 4, 2, seed=22, rope=True, q_shift=0.5)
+    Qc, Kc, Vc = Q.cuda(), K.cuda(), V.cuda()
+    tok_major = HeadShardedAnchorAttn(difference=9.5)(Qc, Kc, Vc)          # [B,N,H,D]
+    base = anchor_attn(Qc, Kc, Vc, difference=9.5, return_computational_ratio=False)
+    assert tok_major.shape == (1, 4096, 4, 128)
+    assert torch.equal(tok_major.permute(0, 2, 1, 3), base)
