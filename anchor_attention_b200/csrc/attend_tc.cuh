@@ -57,6 +57,40 @@ struct TcArgs {
     int32_t* status;
 };
 
+// Tuning knobs (compile-time; the defaults are the measured best on B200: with the two
+// query tiles alternating on one tensor pipe the softmax is bound by instruction issue
+// as much as by the MUFU unit, so moving exponentials to the FMA pipe did not pay).
+#ifndef AA_POLY_SHARE
+#define AA_POLY_SHARE 0
+#endif
+#ifndef AA_SPLIT_P
+#define AA_SPLIT_P 1
+#endif
+constexpr int kPolyShare = AA_POLY_SHARE;   // element pairs out of every 4 whose exp2 is a polynomial (0..4)
+constexpr bool kSplitP = AA_SPLIT_P != 0;   // signal the first half of P early so that P V can start on it
+
+// 2^x for a pair of fp32 values on the FMA pipe: x = n + f with n = floor(x);
+// 2^f from a cubic (max relative error 8.6e-5, far below the bf16 rounding of P),
+// 2^n by adding n to the exponent field.  Inputs below -126 are clamped.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    const float kMagic = 12582912.0f;   // 1.5 * 2^23: adding it leaves floor(x) in the low mantissa bits
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    unsigned long long xi = *reinterpret_cast<unsigned long long*>(&x), fli;
+    const float2 magic2 = make_float2(kMagic, kMagic);
+    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(fli) : "l"(xi), "l"(*reinterpret_cast<const unsigned long long*>(&magic2)));
+    const float2 fl = *reinterpret_cast<float2*>(&fli);
+    const float2 n = __fadd2_rn(fl, make_float2(-kMagic, -kMagic));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 p = __ffma2_rn(make_float2(0.07706617563962936f, 0.07706617563962936f), f,
+                          make_float2(0.22764593362808228f, 0.22764593362808228f));
+    p = __ffma2_rn(p, f, make_float2(0.6951165795326233f, 0.6951165795326233f));
+    p = __ffma2_rn(p, f, make_float2(1.f, 1.f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(fl.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(fl.y) << 23));
+    return p;
+}
+
 // byte offset of (row, 16-byte chunk) inside a 32 KB tile made of two 128B-swizzled slabs
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * kSlabBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
@@ -90,9 +124,10 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     auto s_full = [&](int j) { return bars + 96u + 8u * j; };
     auto p_ready = [&](int j) { return bars + 112u + 8u * j; };
     auto o_done = [&](int j) { return bars + 128u + 8u * j; };
-    const uint32_t tmem_slot_u = bars + 144u;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemQ + kSmemRing + 144);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 148);
+    auto p_ready2 = [&](int j) { return bars + 144u + 8u * j; };
+    const uint32_t tmem_slot_u = bars + 160u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemQ + kSmemRing + 160);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 164);
 
     // ---- which work item ----
     const int BH = a.B * a.H;
@@ -130,6 +165,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             mbar_init(q_full(j), 128);
             mbar_init(s_full(j), 1);
             mbar_init(p_ready(j), 128);
+            mbar_init(p_ready2(j), 128);
             mbar_init(o_done(j), 1);
         }
         *abort_flag = 0;
@@ -278,18 +314,22 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     const int e = c * 64 + 2 * i;
                     const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
                                                             __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
-                    const float2 p = make_float2(fast_exp2(d.x), fast_exp2(d.y));
+                    // kPolyShare of every 4 element pairs take the polynomial on the FMA pipe,
+                    // the others the MUFU unit: both pipes are busy
+                    const float2 p = ((i & 3) < kPolyShare) ? exp2_poly2(d) : make_float2(fast_exp2(d.x), fast_exp2(d.y));
                     rs[i & 3] = __fadd2_rn(rs[i & 3], p);
                     pk[i] = pack_bf16x2(p.x, p.y);
                 }
                 tmem_st32(tS + c * 32, pk);
+                // the first 64 columns of P are enough for the first four k-steps of P V
+                if (kSplitP || c == 1) {
+                    tmem_wait_st();
+                    tcgen05_fence_before();
+                    mbar_arrive((kSplitP && c == 1) ? p_ready2(j) : p_ready(j));
+                }
             }
             const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
-            const float rs_total = rsum.x + rsum.y;
-            l += rs_total;
-            tmem_wait_st();
-            tcgen05_fence_before();
-            mbar_arrive(p_ready(j));
+            l += rsum.x + rsum.y;
         }
 
         // ---- epilogue ----
@@ -348,60 +388,79 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         }
     } else {
         setmaxnreg_dec<88>();
-        if (warp == 8 && lane == 0 && ntiles > 0) {
+        if (warp == 8 && ntiles > 0) {
+            const bool issuer = elect_one();
             // =================================================== MMA issuer
             constexpr uint32_t kIdescQK = idesc_bf16_128x128(0);
             constexpr uint32_t kIdescPV = idesc_bf16_128x128(1);
-            const uint32_t q_u[2] = {s_u, s_u + (uint32_t)kTileBytes};
+            // descriptors: high word constant (8-row group stride 1024 B, version 1, 128B swizzle);
+            // low word = start address / 16 | leading offset / 16 << 16; advancing inside a
+            // tile only adds to the start-address field
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            auto desc = [&](uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; };
+            auto lo_kmajor = [&](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };
+            auto lo_mnmajor = [&](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | ((uint32_t)(kSlabBytes >> 4) << 16); };
+            const uint32_t q_lo[2] = {lo_kmajor(s_u), lo_kmajor(s_u + (uint32_t)kTileBytes)};
             auto slot_addr = [&](int n) { return ring_u + (uint32_t)(n % kStages) * kTileBytes; };
             auto issue_qk = [&](int j, uint32_t kaddr) {
+                const uint32_t k_lo = lo_kmajor(kaddr);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (uint32_t)((ks >> 2) * kSlabBytes + (ks & 3) * 32);
-                    mma_ss(tmem_base + (uint32_t)j * 128u, smem_desc_sw128(q_u[j] + off, 16),
-                           smem_desc_sw128(kaddr + off, 16), kIdescQK, ks > 0);
+                    const uint32_t off = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
+                    if (issuer)
+                        mma_ss(tmem_base + (uint32_t)j * 128u, desc(q_lo[j] + off), desc(k_lo + off), kIdescQK, ks > 0);
                 }
             };
-            auto issue_pv = [&](int j, uint32_t vaddr, bool acc) {
+            auto issue_pv = [&](int j, uint32_t vaddr, bool acc, int ks0) {
+                const uint32_t v_lo = lo_mnmajor(vaddr);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_ts(tmem_base + 256u + (uint32_t)j * 128u, tmem_base + (uint32_t)j * 128u + (uint32_t)ks * 8u,
-                           smem_desc_sw128(vaddr + (uint32_t)ks * 2048u, kSlabBytes), kIdescPV, (ks > 0) || acc);
+                for (int ks = ks0; ks < ks0 + 4; ++ks)
+                    if (issuer)
+                        mma_ts(tmem_base + 256u + (uint32_t)j * 128u, tmem_base + (uint32_t)j * 128u + (uint32_t)ks * 8u,
+                               desc(v_lo + (uint32_t)ks * (2048u >> 4)), kIdescPV, (ks > 0) || acc);
             };
-            bool ok = mbar_wait(q_full(0), 0, abort_flag) && mbar_wait(q_full(1), 0, abort_flag) &&
-                      mbar_wait(kv_full(0), 0, abort_flag);
+            auto wait_all = [&](uint32_t bar, uint32_t parity) {
+                return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+            };
+            bool ok = wait_all(q_full(0), 0) && wait_all(q_full(1), 0) && wait_all(kv_full(0), 0);
             if (ok) {
                 fence_proxy_async();
                 tcgen05_fence_after();
                 issue_qk(0, slot_addr(0));
-                mma_commit(s_full(0));
+                commit_if(issuer, s_full(0));
                 issue_qk(1, slot_addr(0));
-                mma_commit(s_full(1));
-                mma_commit(kv_empty(0));
+                commit_if(issuer, s_full(1));
+                commit_if(issuer, kv_empty(0));
             }
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int nv = 2 * t + 1, nk = 2 * t + 2;
-                ok = mbar_wait(kv_full(nv % kStages), (nv / kStages) & 1, abort_flag);
+                ok = wait_all(kv_full(nv % kStages), (nv / kStages) & 1);
                 if (!ok) break;
                 fence_proxy_async();
                 for (int j = 0; j < 2 && ok; ++j) {
-                    ok = mbar_wait(p_ready(j), t & 1, abort_flag);
+                    ok = wait_all(p_ready(j), t & 1);
                     if (!ok) break;
                     tcgen05_fence_after();
-                    issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe));
-                    if (j == 1) mma_commit(kv_empty(nv % kStages));
+                    issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe), 0);
+                    if (kSplitP) {
+                        ok = wait_all(p_ready2(j), t & 1);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                    }
+                    issue_pv(j, slot_addr(nv), true, 4);
+                    if (j == 1) commit_if(issuer, kv_empty(nv % kStages));
                     if (t + 1 < ntiles) {
                         if (j == 0) {
-                            ok = mbar_wait(kv_full(nk % kStages), (nk / kStages) & 1, abort_flag);
+                            ok = wait_all(kv_full(nk % kStages), (nk / kStages) & 1);
                             if (!ok) break;
                             fence_proxy_async();
                             tcgen05_fence_after();
                         }
                         issue_qk(j, slot_addr(nk));
-                        mma_commit(s_full(j));
-                        if (j == 1) mma_commit(kv_empty(nk % kStages));
+                        commit_if(issuer, s_full(j));
+                        if (j == 1) commit_if(issuer, kv_empty(nk % kStages));
                     } else {
-                        mma_commit(o_done(j));
+                        commit_if(issuer, o_done(j));
                     }
                 }
             }

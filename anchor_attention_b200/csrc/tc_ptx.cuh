@@ -164,6 +164,20 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                  : "memory");
 }
 
+// One lane of a converged warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void commit_if(bool issuer, uint32_t bar) {
+    if (issuer) mma_commit(bar);
+}
+
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));

@@ -95,7 +95,9 @@ def test_against_reference_gpu_fixtures(lib, path):
     call.check_status()
     assert (call.M.cpu()[0] - torch.from_numpy(g["M"])).abs().max() < 1e-4
     assert ((call.L.cpu()[0] - torch.from_numpy(g["L"])).abs() / torch.from_numpy(g["L"])).max() < 1e-4
-    assert (call.Acc.cpu()[0, :, ::16] - torch.from_numpy(g["Acc_rows16"])).abs().max() < 5e-3
+    acc, acc_ref = call.Acc.cpu()[0, :, ::16], torch.from_numpy(g["Acc_rows16"])
+    row_scale = acc_ref.abs().amax(dim=-1, keepdim=True).clamp_min(1.0)
+    assert ((acc - acc_ref).abs() / row_scale).max() < 1e-2     # both sides round P to bf16 (2^-9 each)
     ours = call.id_lists()
     pos = diff = total = 0
     Mref = torch.from_numpy(g["M"])
@@ -201,7 +203,8 @@ def test_full_size_sampled_blocks_and_properties(lib):
     o2 = AnchorAttnCall(Qc, Kc, V2, None, 128, 16, 12.0, workspace=torch.empty_like(call.workspace)).run().float()
     o12 = AnchorAttnCall(Qc, Kc, (Vc.float() + V2.float()).to(torch.bfloat16), None, 128, 16, 12.0,
                          workspace=torch.empty_like(call.workspace)).run().float()
-    assert (o12 - (o1 + o2)).abs().max() < 3e-2
+    # three bf16-rounded outputs and a bf16-rounded V sum: a few ulps of the operands
+    assert ((o12 - (o1 + o2)).abs() / (1 + o1.abs() + o2.abs())).max() < 2e-2
     # oracle on sampled big blocks
     outc = out.float().cpu()
     for h, b in ((0, 0), (13, 7), (31, 15)):
