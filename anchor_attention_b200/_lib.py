@@ -16,8 +16,9 @@ EXPORTS = [
     "aa_workspace_bytes", "aa_workspace_layout", "aa_id_row_offset", "aa_forward",
     "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
-    "aa_launches_per_forward",
+    "aa_launches_per_forward", "aa_step2_stripes_static",
 ]
+STATIC_SCRATCH_BYTES = 8 << 20
 
 
 class AAParams(ctypes.Structure):
@@ -41,6 +42,19 @@ class AALayout(ctypes.Structure):
         "ids_off", "status_off", "total_bytes")] + [("ids_per_head", ctypes.c_int64)]
 
 
+class AAStripesStaticArgs(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+        ("N", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("block_size", ctypes.c_int32), ("step", ctypes.c_int32), ("dtype", ctypes.c_int32),
+        ("theta", ctypes.c_double), ("sm_scale", ctypes.c_double),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p),
+        ("q_stride_b", ctypes.c_int64), ("q_stride_h", ctypes.c_int64), ("q_stride_n", ctypes.c_int64),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_h", ctypes.c_int64), ("k_stride_n", ctypes.c_int64),
+        ("anchors", ctypes.c_void_p), ("counts", ctypes.c_void_p), ("ids", ctypes.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -62,6 +76,8 @@ def load():
     for name in ("aa_forward", "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status"):
         getattr(lib, name).argtypes = [P, ctypes.c_void_p]
         getattr(lib, name).restype = ctypes.c_int
+    lib.aa_step2_stripes_static.argtypes = [ctypes.POINTER(AAStripesStaticArgs), ctypes.c_void_p]
+    lib.aa_step2_stripes_static.restype = ctypes.c_int
     lib.aa_total_selected.argtypes = [P, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
     lib.aa_strerror.argtypes = [ctypes.c_int]
     lib.aa_strerror.restype = ctypes.c_char_p

@@ -5,6 +5,7 @@
 
 #include <stdio.h>
 #include <math.h>
+#include <mutex>
 #include <stdlib.h>
 #include <string.h>
 
@@ -346,6 +347,113 @@ int aa_total_selected(const aa_params_t* p, void* stream, int64_t* total) {
     for (size_t i = 0; i < n; ++i) s += host[i];
     free(host);
     *total = s;
+    return AA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// aa_step2_stripes_static: stripe identification with its intermediates in a
+// fixed array inside the library image, for hosts that may not allocate device
+// memory when they call us (see the header).  Same three kernels as
+// aa_step2_stripes, so counts and ids come out bit-identical.
+// ---------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+// The scratch itself.  In host code this name is only a handle for the runtime's
+// symbol table, never a device pointer; kernels get the address that
+// cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) unsigned char g_static_scratch[AA_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_mutex;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int static_scratch_for_current_device(void** addr, int* dev_out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return AA_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (!p) return AA_ERR_CUDA;
+        g_static_scratch_addr[dev] = p;
+    }
+    *addr = g_static_scratch_addr[dev];
+    *dev_out = dev;
+    return AA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
+    if (!a) return AA_ERR_NULL;
+    aa_params_t shape;
+    memset(&shape, 0, sizeof(shape));
+    shape.B = a->B; shape.H = a->H; shape.Hkv = a->Hkv; shape.N = a->N; shape.D = a->D;
+    shape.block_size = a->block_size; shape.step = a->step; shape.dtype = a->dtype;
+    int rc = check_shape(&shape);
+    if (rc) return rc;
+    if (!a->q || !a->k || !a->anchors || !a->counts || !a->ids) return AA_ERR_NULL;
+    const int64_t st[] = {a->q_stride_b, a->q_stride_h, a->q_stride_n, a->k_stride_b, a->k_stride_h, a->k_stride_n};
+    for (int64_t x : st)
+        if (!stride_ok(x)) return AA_ERR_STRIDE;
+    if (((uintptr_t)a->q | (uintptr_t)a->k) & 15) return AA_ERR_STRIDE;
+
+    // carve the three intermediates out of the fixed array; refuse what does not fit
+    const size_t BH = (size_t)a->B * a->H, nblk = (size_t)a->N / 128;
+    const int NB = a->N / (a->block_size * a->step);
+    const size_t qpool_off = 0;
+    const size_t apool_off = align_up(qpool_off + BH * nblk * aa::kRowBytes);
+    const size_t bitmap_off = align_up(apool_off + BH * nblk * sizeof(float));
+    const size_t need = align_up(bitmap_off + BH * (size_t)NB * ((size_t)a->N / 32) * sizeof(uint32_t));
+    if (need > AA_STATIC_SCRATCH_BYTES) return AA_ERR_TOO_LARGE;
+
+    void* base = nullptr;
+    int dev = 0;
+    rc = static_scratch_for_current_device(&base, &dev);
+    if (rc) return rc;
+    unsigned char* sc = static_cast<unsigned char*>(base);
+    __nv_bfloat16* qpool = reinterpret_cast<__nv_bfloat16*>(sc + qpool_off);
+    float* apool = reinterpret_cast<float*>(sc + apool_off);
+    uint32_t* bitmap = reinterpret_cast<uint32_t*>(sc + bitmap_off);
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int Hg = a->H / a->Hkv;
+    const double sm = a->sm_scale != 0.0 ? a->sm_scale : 1.0 / sqrt((double)a->D);
+    const float qk_scale = (float)(sm * 1.44269504);
+    const float diff = (float)(a->theta * 1.44269504);
+    const int64_t ids_per_head = aa_id_row_offset(a->block_size, a->step, NB);
+
+    aa::pool_kernel<<<dim3(a->N / 128, a->H, a->B), 64, 0, s>>>(
+        view(a->q, a->q_stride_b, a->q_stride_h, a->q_stride_n), a->anchors, qpool, apool, a->H, a->N);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch pool (static)");
+    if (NB > 1) {
+        const size_t smem = (size_t)Hg * a->step * aa::kRowBytes + 2 * 128 * aa::kRowBytes;
+        if (smem > 227 * 1024) return AA_ERR_TOO_LARGE;
+        // Raise the kernel's dynamic shared-memory ceiling to the hardware maximum on every
+        // call: the workspace-based entry point adjusts the same attribute to its own needs,
+        // and this way neither can leave the other with too little.  Not an allocation.
+        e = cudaFuncSetAttribute(aa::score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(score, static)");
+        const int max_tiles = (NB - 1) * a->step - 2;
+        dim3 grid((max_tiles + aa::kTilesPerCta - 1) / aa::kTilesPerCta, NB - 1, a->B * a->Hkv);
+        aa::score_kernel<<<grid, 128, smem, s>>>(view(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_n), qpool, apool,
+                                                 bitmap, a->H, a->Hkv, a->N, a->step, qk_scale, diff);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "launch score (static)");
+    }
+    aa::compact_kernel<<<dim3(NB, a->H, a->B), 256, 0, s>>>(bitmap, a->ids, a->counts, a->H, a->N, a->step,
+                                                           ids_per_head);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch compact (static)");
     return AA_OK;
 }
 

@@ -126,6 +126,54 @@ int aa_check_status(const aa_params_t *p, void *stream);
  * reference's sparsity ratio (anchor_attn_v4.py:271). */
 int aa_total_selected(const aa_params_t *p, void *stream, int64_t *total);
 
+/*
+ * Stripe identification for callers that must not allocate device memory.
+ * (No counterpart in the reference: its step 2 allocates fresh tensors on every
+ * call, get_mask_test.py:138-145.)
+ *
+ * Some hosts of this library are not allowed to obtain scratch memory at call
+ * time: an inference-runtime plug-in whose enqueue hook is forbidden from
+ * allocating, or a process whose whole device memory has already been handed to
+ * a framework's arena, where a raw allocation would fail.  For them this entry
+ * point does the same work as aa_step2_stripes -- same kernels, same bits in
+ * `counts` and `ids` -- but keeps its intermediates (pooled queries, pooled
+ * anchors, hit bitmap) in a fixed AA_STATIC_SCRATCH_BYTES array that is part of
+ * the library image.  Every GPU that loads the library carries that array until
+ * the process exits.
+ *
+ * The caller passes q, k, the step-1 row maxima `anchors` (fp32 [B,H,N], log2
+ * domain) and the two output buffers: counts int32 [B,H,NB] and ids int32
+ * [B,H,ids_per_head] (ids_per_head = aa_id_row_offset(block_size, step, NB)).
+ *
+ * - Problems whose intermediates exceed the array are refused with
+ *   AA_ERR_TOO_LARGE; nothing is launched.  The need is
+ *   B*H*(N/128)*(256+4) + B*H*NB*(N/32)*4 bytes plus alignment padding, e.g.
+ *   4.1 MiB for B*H = 32, N = 32768.
+ * - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * - The first call on a device looks up the array's device address (once per
+ *   device, with that device current); make that first call before starting
+ *   any stream capture.
+ * - All calls share the one array and it keeps whatever the last call left in
+ *   it.  Nothing in it has to start at zero (every word a kernel reads is
+ *   written earlier in the same call), but two calls that overlap on the GPU --
+ *   different streams, or different host threads -- race on it: serialise them.
+ */
+#define AA_STATIC_SCRATCH_BYTES (8u << 20)
+
+typedef struct aa_stripes_static_args {
+    int32_t B, H, Hkv, N, D;
+    int32_t block_size, step, dtype;          /* as in aa_params_t                 */
+    double  theta, sm_scale;                  /* as in aa_params_t                 */
+    const void *q, *k;                        /* bf16 device pointers              */
+    int64_t q_stride_b, q_stride_h, q_stride_n;
+    int64_t k_stride_b, k_stride_h, k_stride_n;
+    const float *anchors;                     /* in:  [B,H,N] step-1 row maxima    */
+    int32_t *counts;                          /* out: [B,H,NB]                     */
+    int32_t *ids;                             /* out: [B,H,ids_per_head]           */
+} aa_stripes_static_args_t;
+
+int aa_step2_stripes_static(const aa_stripes_static_args_t *args, void *stream);
+
 const char *aa_strerror(int code);
 /* Text of the last CUDA error this library saw on the calling thread. */
 const char *aa_last_cuda_error(void);
