@@ -161,6 +161,39 @@ int make_kv_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, int64
     return AA_OK;
 }
 
+// The same tensor seen as a 2-D matrix of rows of `sn` elements, for TMA row gathers
+// (tile::gather4): box = 64 elements of one row, 128-byte swizzle.  Row id n of (batch z,
+// head g) is matrix row (z*sb + g*sh) / sn + n, starting at column (z*sb + g*sh) % sn.
+// Possible when every head's 128 columns lie inside one matrix row; *usable says so.
+int make_gather_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, int64_t sn, int B, int heads, int N,
+                    int* usable) {
+    *usable = 0;
+    memset(map, 0, sizeof(*map));
+    const char* mode = getenv("AA_GATHER");            // "cp_async" forces the per-thread gather (for A/B timing)
+    if (mode && strcmp(mode, "cp_async") == 0) return AA_OK;
+    if (sn < 128 || sb < 0 || sh < 0) return AA_OK;
+    int64_t max_row0 = 0;
+    for (int z = 0; z < B; ++z)
+        for (int g = 0; g < heads; ++g) {
+            const int64_t off = (int64_t)z * sb + (int64_t)g * sh;
+            if (off % sn + 128 > sn) return AA_OK;
+            if (off / sn > max_row0) max_row0 = off / sn;
+        }
+    const int64_t rows = max_row0 + N;
+    if (rows >= ((int64_t)1 << 31) || sn >= ((int64_t)1 << 31)) return AA_OK;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return AA_OK;
+    cuuint64_t gdim[2] = {(cuuint64_t)sn, (cuuint64_t)rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)sn * 2};
+    cuuint32_t box[2] = {64, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) *usable = 1;
+    return AA_OK;
+}
+
 template <int MODE>
 int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
     static thread_local int configured_dev[2] = {-1, -1};
@@ -183,8 +216,17 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     rc = make_kv_map(&vmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.vpos_n,
                      &ta.vpos_h, &ta.vpos_b);
     if (rc) return rc;
+    CUtensorMap kgmap, vgmap;
+    ta.k_gather = ta.v_gather = 0;
+    if (MODE == aa::kStripe) {
+        make_gather_map(&kgmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.k_gather);
+        make_gather_map(&vgmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.v_gather);
+    } else {
+        memset(&kgmap, 0, sizeof(kgmap));
+        memset(&vgmap, 0, sizeof(vgmap));
+    }
     const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / (2 * aa::tc::kTile)));
-    aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, ta);
+    aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, ta);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)" : "launch step3 (tc)");
     return AA_OK;

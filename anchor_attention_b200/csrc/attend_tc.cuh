@@ -16,9 +16,11 @@
 //   warps 0-3   softmax of tile A: thread r owns query row r = tensor-memory lane r
 //   warps 4-7   softmax of tile B
 //   warp  8     MMA issuer (one elected lane): S = Q K^T and O += P V with tcgen05.mma
-//   warp  9     loader: TMA box loads for runs of consecutive rows, 16-byte
-//               cp.async row gathers otherwise, into a 5-slot ring of 32 KB tiles
-//   warps 10-11 idle (they only take part in the register re-allocation)
+//   warps 9-11  loaders: one TMA box load for a run of 128 consecutive rows; discrete
+//               rows are split between TMA row gathers (tile::gather4, four rows per
+//               instruction, warp 9) and 16-byte cp.async copies (warps 10-11; all
+//               three warps for stride patterns no 2-D tensor map covers); into a
+//               5-slot ring of 32 KB tiles
 //
 // Tensor memory (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each.  P (bf16)
 // overwrites the first 64 columns of its S and is consumed from tensor memory as
@@ -38,7 +40,23 @@
 namespace aa {
 namespace tc {
 
-constexpr int kThreads = 384;
+#ifndef AA_LOADER_WARPS
+#define AA_LOADER_WARPS 3
+#endif
+constexpr int kLoaderWarps = AA_LOADER_WARPS;          // warps 9 .. 9 + kLoaderWarps - 1
+constexpr int kThreads = (9 + kLoaderWarps) * 32;
+#ifndef AA_SOFTMAX_REGS
+#define AA_SOFTMAX_REGS 208
+#endif
+#ifndef AA_OTHER_REGS
+#define AA_OTHER_REGS (AA_LOADER_WARPS > 3 ? 48 : 88)
+#endif
+// setmaxnreg only moves registers between the warps of the CTA: what the CTA gets at launch
+// (64 K registers / threads, rounded down to a multiple of 8, per thread) must cover the
+// re-allocated sizes, or the growing warps wait for ever.  Warps re-allocate in groups of four.
+static_assert(kLoaderWarps == 3 || kLoaderWarps == 7, "loader warps must fill whole groups of four warps");
+static_assert(kThreads * (65536 / kThreads / 8 * 8) >= 256 * AA_SOFTMAX_REGS + (kThreads - 256) * AA_OTHER_REGS,
+              "register re-allocation exceeds the CTA's registers");
 constexpr int kStages = 5;
 constexpr int kTile = 128;                        // rows per query tile and per key tile
 constexpr int kTileBytes = kTile * kRowBytes;     // 32 KB
@@ -54,6 +72,7 @@ struct TcArgs {
     AttendArgs a;
     int kpos_n, kpos_h, kpos_b;      // which tensor-map coordinate (1..3 -> 0..2) carries n / head / batch
     int vpos_n, vpos_h, vpos_b;
+    int k_gather, v_gather;          // 1: the 2-D row-gather tensor map of K / V is usable
     int32_t* status;
 };
 
@@ -66,6 +85,10 @@ struct TcArgs {
 #ifndef AA_SPLIT_P
 #define AA_SPLIT_P 1
 #endif
+#ifndef AA_TMA_ROWS
+#define AA_TMA_ROWS 32
+#endif
+constexpr int kTmaRows = AA_TMA_ROWS;       // rows of a gathered tile fetched by TMA row gathers (multiple of 4)
 constexpr int kPolyShare = AA_POLY_SHARE;   // element pairs out of every 4 whose exp2 is a polynomial (0..4)
 constexpr bool kSplitP = AA_SPLIT_P != 0;   // signal the first half of P early so that P V can start on it
 
@@ -107,7 +130,8 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, u
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, TcArgs ta) {
+attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                 const __grid_constant__ CUtensorMap kgmap, const __grid_constant__ CUtensorMap vgmap, TcArgs ta) {
     extern __shared__ uint8_t smem_raw[];
     const AttendArgs& a = ta.a;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -158,7 +182,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     // ---- set-up ----
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(kv_full(i), 32);
+            mbar_init(kv_full(i), 32 * kLoaderWarps);
             mbar_init(kv_empty(i), 1);
         }
         for (int j = 0; j < 2; ++j) {
@@ -182,7 +206,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
 
     if (warp < 8) {
         // =================================================== softmax warps
-        setmaxnreg_inc<208>();
+        setmaxnreg_inc<AA_SOFTMAX_REGS>();
         const int j = warp >> 2;
         const int r = tid & 127;
         const int qb = 2 * pair + j;
@@ -387,7 +411,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             }
         }
     } else {
-        setmaxnreg_dec<88>();
+        setmaxnreg_dec<AA_OTHER_REGS>();
         if (warp == 8 && ntiles > 0) {
             const bool issuer = elect_one();
             // =================================================== MMA issuer
@@ -464,10 +488,16 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     }
                 }
             }
-        } else if (warp == 9 && ntiles > 0) {
-            // =================================================== loader
+        } else if (warp >= 9 && ntiles > 0) {
+            // =================================================== loaders (three warps)
+            const int lw = warp - 9;
             const __nv_bfloat16* kbase = a.k.ptr + z * a.k.sb + kvh * a.k.sh;
             const __nv_bfloat16* vbase = a.v.ptr + z * a.v.sb + kvh * a.v.sh;
+            // row-gather maps see the tensor as rows of `sn` elements: this head's rows start at
+            // row (offset / sn), column (offset % sn)
+            const int64_t koff = z * a.k.sb + kvh * a.k.sh, voff = z * a.v.sb + kvh * a.v.sh;
+            const int k_row0 = (int)(koff / a.k.sn), k_col0 = (int)(koff % a.k.sn);
+            const int v_row0 = (int)(voff / a.v.sn), v_col0 = (int)(voff % a.v.sn);
             bool ok = true;
             for (int n = 0; n < 2 * ntiles && ok; ++n) {
                 const int slot = n % kStages, it = n / kStages;
@@ -492,7 +522,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     }
                 }
                 if (run) {
-                    if (lane == 0) {
+                    if (lw == 0 && lane == 0) {
                         mbar_arrive_expect_tx(kv_full(slot), kTileBytes);
                         if (is_v)
                             tma_tile(dst, &vmap, kv_full(slot), ta.vpos_n, ta.vpos_h, ta.vpos_b, row0, kvh, z);
@@ -501,17 +531,68 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     } else {
                         mbar_arrive(kv_full(slot));
                     }
+                    continue;
+                }
+                // Discrete rows.  The TMA unit and the load/store unit each sustain only about one
+                // 128-byte row segment per 17-24 cycles on gathers, so the tile is split between
+                // them: rows [0, tma_rows) by TMA row gathers from the first loader warp
+                // (tile::gather4, lane i takes rows 4i .. 4i+3, two 64-column halves each), the rest
+                // by 16-byte cp.async copies from the other loader warps (a warp sustains only a few
+                // copies in flight, so the rate grows with the warp count).  Without a usable 2-D
+                // map all loader warps copy.
+                // Slots past the count read row 0 / zero-fill; the softmax masks them.
+                const bool g4 = MODE == kStripe && (is_v ? ta.v_gather : ta.k_gather);
+                const int tma_rows = g4 ? kTmaRows : 0;
+                // this warp's cp.async rows [ra, rb): the non-TMA rows in even-sized shares
+                int ra, rb;
+                {
+                    const int first = g4 ? 1 : 0, nw = kLoaderWarps - first;
+                    const int pairs = (kTile - tma_rows) / 2;              // two rows per copy instruction
+                    const int w = lw - first;
+                    ra = tma_rows + 2 * ((pairs * w) / nw);
+                    rb = tma_rows + 2 * ((pairs * (w + 1)) / nw);
+                    if (w < 0) ra = rb = 0;
+                }
+                if (g4 && lw == 0) {
+                    if (lane == 0)
+                        mbar_arrive_expect_tx(kv_full(slot), (uint32_t)tma_rows * kRowBytes);
+                    else
+                        mbar_arrive(kv_full(slot));
+                    if (4 * lane < tma_rows) {
+                        const int s0 = t * kTile + 4 * lane;
+                        int4 id4 = make_int4(0, 0, 0, 0);
+                        if (s0 + 4 <= count) {
+                            id4 = *reinterpret_cast<const int4*>(idp + s0);
+                        } else {
+                            if (s0 < count) id4.x = idp[s0];
+                            if (s0 + 1 < count) id4.y = idp[s0 + 1];
+                            if (s0 + 2 < count) id4.z = idp[s0 + 2];
+                        }
+                        const CUtensorMap* gm = is_v ? &vgmap : &kgmap;
+                        const int r0 = is_v ? v_row0 : k_row0, c0 = is_v ? v_col0 : k_col0;
+                        const uint32_t d = dst + (uint32_t)lane * 512u;
+                        tma_gather4(d, gm, kv_full(slot), c0, r0 + id4.x, r0 + id4.y, r0 + id4.z, r0 + id4.w);
+                        tma_gather4(d + kSlabBytes, gm, kv_full(slot), c0 + 64, r0 + id4.x, r0 + id4.y, r0 + id4.z,
+                                    r0 + id4.w);
+                    }
                 } else {
                     const __nv_bfloat16* base = is_v ? vbase : kbase;
                     const int64_t sn = is_v ? a.v.sn : a.k.sn;
-                    const int s0 = t * kTile;
+                    const int s0 = t * kTile + ra;
+                    // this warp's ids (at most 64): two coalesced loads, handed round by shuffle
+                    const int id_lo = (ra + lane < rb && s0 + lane < count) ? idp[s0 + lane] : -1;
+                    const int id_hi = (ra + 32 + lane < rb && s0 + 32 + lane < count) ? idp[s0 + 32 + lane] : -1;
+                    const int ch = lane & 15;
+                    const int npairs_rows = (rb - ra) >> 1;
 #pragma unroll 4
-                    for (int i = 0; i < 64; ++i) {
-                        const int id = lane + 32 * i;
-                        const int rr = id >> 4, ch = id & 15;
-                        const bool valid = (s0 + rr) < count;
-                        const int64_t row = valid ? idp[s0 + rr] : 0;
-                        cp_async16(dst + sw_off(rr, ch), base + row * sn + ch * 8, valid ? 16 : 0);
+                    for (int i = 0; i < npairs_rows; ++i) {
+                        const int rel = 2 * i + (lane >> 4);
+                        const int v0 = __shfl_sync(0xffffffffu, id_lo, rel & 31);
+                        const int v1 = __shfl_sync(0xffffffffu, id_hi, rel & 31);
+                        const int row = rel < 32 ? v0 : v1;
+                        const bool valid = row >= 0;
+                        cp_async16(dst + sw_off(ra + rel, ch), base + (int64_t)(valid ? row : 0) * sn + ch * 8,
+                                   valid ? 16 : 0);
                     }
                     cp_async_mbar_arrive_noinc(kv_full(slot));
                 }
