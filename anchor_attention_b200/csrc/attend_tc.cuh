@@ -82,6 +82,9 @@ struct TcArgs {
 #ifndef AA_POLY_SHARE
 #define AA_POLY_SHARE 0
 #endif
+#ifndef AA_ORDER_KV_MAJOR
+#define AA_ORDER_KV_MAJOR 1
+#endif
 #ifndef AA_SPLIT_P
 #define AA_SPLIT_P 1
 #endif
@@ -156,10 +159,23 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     // ---- which work item ----
     const int BH = a.B * a.H;
     const int npairs = a.N / (2 * kTile);
+#if AA_ORDER_KV_MAJOR
+    // CTAs that run at the same time share one KV head: its K and V (2 x 256 B x N) stay in
+    // L2 while the query heads of the group and their query-tile pairs (heaviest first) walk them
+    const int Hg = a.H / a.Hkv;
+    const int per_kv = Hg * npairs;
+    const int kvz = (int)(blockIdx.x / per_kv), rem = (int)(blockIdx.x % per_kv);
+    const int pair = npairs - 1 - rem / Hg;
+    const int z = kvz / a.Hkv, kvh = kvz % a.Hkv;
+    const int h = kvh * Hg + rem % Hg;
+    const int hz = z * a.H + h;
+    (void)BH;
+#else
     const int pair = npairs - 1 - (int)(blockIdx.x / BH);      // heaviest first
     const int hz = blockIdx.x % BH;
     const int z = hz / a.H, h = hz % a.H;
     const int kvh = h / (a.H / a.Hkv);
+#endif
     const int G = 128 * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;

@@ -29,6 +29,11 @@ sys.path.insert(0, ROOT)
 
 H, HKV, D, BLOCK, STEP, THETA = 32, 8, 128, 128, 16, 12.0
 METRIC = "ms_per_layer_anchor_attn_prefill_128k_llama31_8b_heads"
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step-3 launch per K/V tile pair a
+# CTA loads, from an ncu capture at 32768 tokens (2.68 GB for 483,840 tile-pair loads of 64 KB each;
+# profiles/attend_tc_seq32768.md).  The full-size launch is not captured; its traffic is this figure
+# times its tile-pair loads, which assumes the same L2 hit rate.
+STEP3_DRAM_BYTES_PER_TILE_PAIR = 2.68e9 / 483840
 
 
 def algorithmic_flops(N, H, counts_total, step=STEP):
@@ -271,6 +276,8 @@ def run_ours(args):
         cap = H * sum(b * G - 2 * BLOCK for b in range(1, N // G))
         f3_rank = f3 / W                               # the launch timed on one rank handles 1/W of the heads
         achieved = f3_rank / (k3_ms * 1e-3) / 1e12
+        tile_pair_loads = counts_all / W * (G // (2 * BLOCK)) / BLOCK     # ids x 8 query-tile pairs / 128 ids per tile
+        traffic = STEP3_DRAM_BYTES_PER_TILE_PAIR * tile_pair_loads
         line = {
             "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": W, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
@@ -284,7 +291,8 @@ def run_ours(args):
             "layer_tflops": (f1 + f2 + f3) / (ms * 1e-3) / 1e12,
             "roofline": {"kernel": "step 3 (gathered sparse flash attention)", "bound": "tensor",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                         "traffic": None, "peak_source": f"{peak_src} (sustained bf16)", "launch_ms": k3_ms},
+                         "traffic": traffic, "traffic_unit": "bytes per launch (ncu at 32768 tokens, scaled by tile loads)",
+                         "peak_source": f"{peak_src} (sustained bf16)", "launch_ms": k3_ms},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": W * sum(t.numel() * 2 for t in (hq, hk, hv)),
                     "d2h_bytes_per_step": W * hout.numel() * 2, "steps": e2e_steps},
             "gpu_launches": launches_per_forward() * args.steps,
