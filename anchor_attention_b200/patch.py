@@ -85,12 +85,41 @@ def _dense_causal(query, key, value, scaling, q_offset):
     return F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling, enable_gqa=True)
 
 
+_head_parallel_group = None
+_head_parallel_on = False
+
+
+def set_head_parallel_group(group):
+    """Run the sparse part of every patched attention layer head-parallel over the
+    ranks of ``group`` (a torch.distributed process group; ``None`` switches it off):
+    each rank computes its KV-head groups and one all-gather assembles all heads.
+    Every rank must call the model with the same inputs."""
+    global _head_parallel_group, _head_parallel_on
+    _head_parallel_group = group
+    _head_parallel_on = group is not None
+
+
+def _head_parallel_anchor_attn(query, key, value, scaling, block, step, theta, _ratio):
+    """anchor_attn on this rank's heads, then the all-gather; returns [B,H,N,D] (a view
+    of token-major memory)."""
+    import torch.distributed as dist
+    from .ops import AnchorAttnCall
+    from .parallel import gather_heads, head_partition
+    W, rank = dist.get_world_size(_head_parallel_group), dist.get_rank(_head_parallel_group)
+    B, H, N, D = query.shape
+    q_lo, q_hi, kv_lo, kv_hi = head_partition(H, key.shape[1], W, rank)
+    local = torch.empty((B, N, q_hi - q_lo, D), dtype=query.dtype, device=query.device)
+    AnchorAttnCall(query[:, q_lo:q_hi], key[:, kv_lo:kv_hi], value[:, kv_lo:kv_hi], scaling, block, step, theta,
+                   out=local.permute(0, 2, 1, 3)).run()
+    return gather_heads(local, _head_parallel_group).permute(0, 2, 1, 3)
+
+
 def anchor_attention_forward(module, query, key, value, attention_mask=None, scaling: Optional[float] = None,
                              dropout: float = 0.0, anchor_attn_fn=None, **kwargs):
     """Attention function for the transformers attention registry.
     query [B,H,N,D]; key, value [B,Hkv,Nk,D]; returns ([B,N,H,D], None)."""
-    if anchor_attn_fn is None:
-        from .ops import anchor_attn as anchor_attn_fn
+    if anchor_attn_fn is None and _head_parallel_on:
+        anchor_attn_fn = _head_parallel_anchor_attn
     cfg = module.config
     block, step, theta = int(cfg.block_size_M), int(cfg.step), float(cfg.theta)
     B, H, q_len, D = query.shape
@@ -98,7 +127,13 @@ def anchor_attention_forward(module, query, key, value, attention_mask=None, sca
     G = block * step
     out = torch.empty((B, q_len, H, D), dtype=query.dtype, device=query.device)
     n_sparse = (q_len - q_len % G) if (q_len > 1 and q_len == kv_len) else 0
-    if n_sparse:
+    if n_sparse and anchor_attn_fn is None:
+        # the kernels read the [B,N,H,D]-ordered projections through their strides and write
+        # the token-major result in place: no transposes, no repeat_kv
+        from .ops import AnchorAttnCall
+        AnchorAttnCall(query[:, :, :n_sparse], key[:, :, :n_sparse], value[:, :, :n_sparse], scaling, block, step,
+                       theta, out=out[:, :n_sparse].permute(0, 2, 1, 3)).run()
+    elif n_sparse:
         sparse = anchor_attn_fn(query[:, :, :n_sparse], key[:, :, :n_sparse], value[:, :, :n_sparse],
                                 scaling, block, step, theta, False)
         out[:, :n_sparse] = sparse.transpose(1, 2)
@@ -132,7 +167,13 @@ def patch_model(model, pattern: str, config=None):
     patch_model_config(model, pattern, config)
     AttentionInterface.register(ATTN_IMPLEMENTATION_NAME, anchor_attention_forward)
     model.config._attn_implementation = ATTN_IMPLEMENTATION_NAME
-    # memory patch the reference applies with every pattern: the MLP in 32768-token chunks
+    install_chunked_mlp(model)
+    return model
+
+
+def install_chunked_mlp(model):
+    """The memory patch the reference applies with every pattern: each MLP runs in
+    32768-token chunks (anchor_attn/src/modules/llama/llama_mlp_forward.py:49-56)."""
     for mod in model.modules():
         if type(mod).__name__.endswith("MLP") and not getattr(mod, "_anchor_chunked", False):
             mod.forward = _chunked_mlp_forward(mod)
