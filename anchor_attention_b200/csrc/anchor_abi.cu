@@ -11,6 +11,7 @@
 
 #include "attend_tc.cuh"
 #include "common.cuh"
+#include "score_tc.cuh"
 #include "stripe.cuh"
 
 namespace {
@@ -232,6 +233,63 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     return AA_OK;
 }
 
+// Pooled queries [B*H, N/128, 128] bf16 (contiguous) as a 3-D tensor map; box = 64 elements x
+// `step` rows (the pooled rows of one query head and big block), 128-byte swizzle.
+int make_qpool_map(CUtensorMap* map, const void* qpool, int BH, int N, int step) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+        return AA_ERR_CUDA;
+    }
+    const cuuint64_t rows = (cuuint64_t)N / 128;
+    cuuint64_t gdim[3] = {128, rows, (cuuint64_t)BH};
+    cuuint64_t gstr[2] = {256, rows * 256};
+    cuuint32_t box[3] = {64, (cuuint32_t)step, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(qpool), gdim, gstr, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled(qpool) failed with CUresult %d", (int)r);
+        return AA_ERR_CUDA;
+    }
+    return AA_OK;
+}
+
+// The scoring pass of step 2 (csrc/score_tc.cuh) for NB > 1.
+int launch_score(const void* k, int64_t ksb, int64_t ksh, int64_t ksn, const __nv_bfloat16* qpool, const float* apool,
+                 uint32_t* bitmap, int32_t* status, int B, int H, int Hkv, int N, int step, float qk_scale, float diff,
+                 cudaStream_t st) {
+    if (!(qk_scale > 0.f)) return AA_ERR_SHAPE;      // the kernel relies on scores growing with the dot product
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (configured_dev != dev) {
+        e = cudaFuncSetAttribute(aa::sc::score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 aa::sc::kScSmemTotal);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(score_tc)");
+        configured_dev = dev;
+    }
+    aa::sc::ScoreArgs sa;
+    sa.apool = apool; sa.bitmap = bitmap; sa.B = B; sa.H = H; sa.Hkv = Hkv; sa.N = N; sa.step = step;
+    sa.qk_scale = qk_scale; sa.diff = diff; sa.status = status;
+    CUtensorMap kmap, qmap;
+    int rc = make_kv_map(&kmap, k, ksb, ksh, ksn, B, Hkv, N, &sa.kpos_n, &sa.kpos_h, &sa.kpos_b);
+    if (rc) return rc;
+    rc = make_qpool_map(&qmap, qpool, B * H, N, step);
+    if (rc) return rc;
+    const int NB = N / (128 * step), Hg = H / Hkv;
+    const int max_tiles = (NB - 1) * step - 2;
+    const int units_per_cta = 2 * (128 / step);
+    dim3 grid((max_tiles + aa::sc::kTilesPerCta - 1) / aa::sc::kTilesPerCta,
+              ((NB - 1) * Hg + units_per_cta - 1) / units_per_cta, B * Hkv);
+    aa::sc::score_tc_kernel<<<grid, aa::sc::kScThreads, aa::sc::kScSmemTotal, st>>>(kmap, qmap, sa);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch score");
+    return AA_OK;
+}
+
 template <int MODE>
 int launch_attend(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
     return launch_attend_tc<MODE>(p, lay, st);
@@ -293,7 +351,6 @@ int aa_step2_stripes(const aa_params_t* p, void* stream) {
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int NB = p->N / (p->block_size * p->step);
-    const int Hg = p->H / p->Hkv;
     const double sm = scale_of(p);
     // the reference forms both constants in double precision on the host and passes
     // them to the kernel as fp32 (anchor_attn_v4.py:298, get_mask_test.py:86)
@@ -313,25 +370,9 @@ int aa_step2_stripes(const aa_params_t* p, void* stream) {
     if (e != cudaSuccess) return cuda_fail(e, "launch pool");
 
     if (NB > 1) {
-        const size_t smem = (size_t)Hg * p->step * aa::kRowBytes + 2 * 128 * aa::kRowBytes;
-        if (smem > 227 * 1024) return AA_ERR_TOO_LARGE;
-        static thread_local int configured_dev = -1;
-        static thread_local size_t configured_smem = 0;
-        int dev = 0;
-        e = cudaGetDevice(&dev);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-        if (configured_dev != dev || configured_smem < smem) {
-            e = cudaFuncSetAttribute(aa::score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(score)");
-            configured_dev = dev;
-            configured_smem = smem;
-        }
-        const int max_tiles = (NB - 1) * p->step - 2;
-        dim3 grid((max_tiles + aa::kTilesPerCta - 1) / aa::kTilesPerCta, NB - 1, p->B * p->Hkv);
-        aa::score_kernel<<<grid, 128, smem, st>>>(view(p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n), qpool,
-                                                  apool, bitmap, p->H, p->Hkv, p->N, p->step, qk_scale, diff);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return cuda_fail(e, "launch score");
+        int rc2 = launch_score(p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, qpool, apool, bitmap,
+                               ws_ptr<int32_t>(p, lay.status_off), p->B, p->H, p->Hkv, p->N, p->step, qk_scale, diff, st);
+        if (rc2) return rc2;
     }
     aa::compact_kernel<<<dim3(NB, p->H, p->B), 256, 0, st>>>(bitmap, ids, counts, p->H, p->N, p->step,
                                                             lay.ids_per_head);
@@ -455,7 +496,7 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     const size_t apool_off = align_up(qpool_off + BH * nblk * aa::kRowBytes);
     const size_t bitmap_off = align_up(apool_off + BH * nblk * sizeof(float));
     const size_t need = align_up(bitmap_off + BH * (size_t)NB * ((size_t)a->N / 32) * sizeof(uint32_t));
-    if (need > AA_STATIC_SCRATCH_BYTES) return AA_ERR_TOO_LARGE;
+    if (need + 256 > AA_STATIC_SCRATCH_BYTES) return AA_ERR_TOO_LARGE;      // + the status word at the end
 
     void* base = nullptr;
     int dev = 0;
@@ -467,7 +508,6 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(sc + bitmap_off);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int Hg = a->H / a->Hkv;
     const double sm = a->sm_scale != 0.0 ? a->sm_scale : 1.0 / sqrt((double)a->D);
     const float qk_scale = (float)(sm * 1.44269504);
     const float diff = (float)(a->theta * 1.44269504);
@@ -478,19 +518,13 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch pool (static)");
     if (NB > 1) {
-        const size_t smem = (size_t)Hg * a->step * aa::kRowBytes + 2 * 128 * aa::kRowBytes;
-        if (smem > 227 * 1024) return AA_ERR_TOO_LARGE;
-        // Raise the kernel's dynamic shared-memory ceiling to the hardware maximum on every
-        // call: the workspace-based entry point adjusts the same attribute to its own needs,
-        // and this way neither can leave the other with too little.  Not an allocation.
-        e = cudaFuncSetAttribute(aa::score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(score, static)");
-        const int max_tiles = (NB - 1) * a->step - 2;
-        dim3 grid((max_tiles + aa::kTilesPerCta - 1) / aa::kTilesPerCta, NB - 1, a->B * a->Hkv);
-        aa::score_kernel<<<grid, 128, smem, s>>>(view(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_n), qpool, apool,
-                                                 bitmap, a->H, a->Hkv, a->N, a->step, qk_scale, diff);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return cuda_fail(e, "launch score (static)");
+        // the status word of the bounded device-side waits lives at the end of the fixed array
+        int32_t* status = reinterpret_cast<int32_t*>(sc + AA_STATIC_SCRATCH_BYTES - 256);
+        cudaError_t em = cudaMemsetAsync(status, 0, sizeof(int32_t), s);
+        if (em != cudaSuccess) return cuda_fail(em, "cudaMemsetAsync(static status)");
+        int rc2 = launch_score(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_n, qpool, apool, bitmap, status, a->B,
+                               a->H, a->Hkv, a->N, a->step, qk_scale, diff, s);
+        if (rc2) return rc2;
     }
     aa::compact_kernel<<<dim3(NB, a->H, a->B), 256, 0, s>>>(bitmap, a->ids, a->counts, a->H, a->N, a->step,
                                                            ids_per_head);

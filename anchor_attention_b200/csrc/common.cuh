@@ -1,4 +1,4 @@
-// Shared device helpers: bf16 rounding, cp.async, ldmatrix, mma.sync, fast exp2.
+// Shared device helpers: bf16 rounding, cp.async, fast exp2, the argument structs.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -68,34 +68,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
-                                                  uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-
-// D += A(16x16, row) * B(16x8, col), bf16 inputs, fp32 accumulate.
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// Shared-memory tiles hold rows of 128 bf16 (256 B = 16 chunks of 16 B).  Chunk c
-// of row r is stored at chunk slot c ^ (r & 7) so that ldmatrix reads of eight
-// consecutive rows hit eight different bank groups.
-__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
-    return static_cast<uint32_t>(row * kRowBytes + ((chunk ^ (row & 7)) << 4));
 }
 
 }  // namespace aa

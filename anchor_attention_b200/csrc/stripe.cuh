@@ -3,12 +3,11 @@
 // Replaces get_q_mask_triton (reference: anchor_attn/src/ops/get_mask_test.py:7-124).
 // Three kernels:
 //   pool_kernel     block-mean queries (bf16 running sum in the reference's add
-//                   order) and block-mean anchors
-//   score_kernel    streams the key columns once per (KV head, big block); the
-//                   pooled rows of all query heads of the KV group are compared
-//                   against each key tile, so the key stream is shared by the
-//                   group.  Emits one hit bit per (query head, big block, column).
-//   compact_kernel  ordered compaction of the hit bitmap into ascending id lists.
+//                   order) and block-mean anchors                       (this file)
+//   score_tc_kernel pooled rows against the key columns on the tensor cores; emits
+//                   one hit bit per (query head, big block, column)     (score_tc.cuh)
+//   compact_kernel  ordered compaction of the hit bitmap into ascending id lists
+//                                                                       (this file)
 #pragma once
 #include "common.cuh"
 
@@ -62,124 +61,6 @@ __global__ void __launch_bounds__(64) pool_kernel(TensorView q, const float* __r
 }
 
 // ---------------------------------------------------------------------------
-// score_kernel
-//   grid  (ceil(max_tiles / kTilesPerCta), NB - 1, B * Hkv), 128 threads.
-//   CTA (c, b-1, z*Hkv+kvh) handles key tiles t = 1 + c*kTilesPerCta ... of big
-//   block b (tile t = columns [128 t, 128 t + 128)); candidates of big block b
-//   are tiles 1 .. b*step - 2  (get_mask_test.py:93-94).
-//   Warp w owns columns 32 w .. 32 w + 31 of each tile and all pooled rows.
-//   score = bf16(dot * fp32(sm_scale * log2e)); hit = fp32(score) + diff >= anchor.
-//   bitmap[(z,h,b)][col / 32] bit (col % 32).
-// Dynamic shared memory: pooled queries of the group (Hg * step rows) then two
-// key tiles of 32 KB.
-// ---------------------------------------------------------------------------
-constexpr int kTilesPerCta = 8;
-
-__global__ void __launch_bounds__(128) score_kernel(TensorView k, const __nv_bfloat16* __restrict__ qpool,
-                                                    const float* __restrict__ apool, uint32_t* __restrict__ bitmap,
-                                                    int H, int Hkv, int N, int step, float qk_scale, float diff) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int b = blockIdx.y + 1;
-    const int z = blockIdx.z / Hkv, kvh = blockIdx.z % Hkv;
-    const int Hg = H / Hkv;
-    const int ntiles = b * step - 2;
-    const int t_begin = 1 + blockIdx.x * kTilesPerCta;
-    if (t_begin > ntiles) return;
-    const int t_end = min(t_begin + kTilesPerCta, ntiles + 1);   // exclusive
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NB = N / (128 * step);
-    const int prow_per_head = N / 128;
-
-    uint8_t* sq = smem;                                  // [Hg*step][128] bf16, swizzled
-    const int qrows = Hg * step;
-    uint8_t* sk = smem + (size_t)qrows * kRowBytes;      // 2 x [128][128] bf16, swizzled
-    const uint32_t sq_u = smem_u32(sq), sk_u = smem_u32(sk);
-
-    // pooled queries of the group -> shared
-    for (int c = tid; c < qrows * 16; c += 128) {
-        const int r = c >> 4, ch = c & 15;
-        const int g = r / step, j = r % step;
-        const int64_t prow = (int64_t)(z * H + kvh * Hg + g) * prow_per_head + b * step + j;
-        cp_async16(sq_u + tile_off(r, ch), qpool + prow * kD + ch * 8, 16);
-    }
-    const __nv_bfloat16* kbase = k.ptr + z * k.sb + kvh * k.sh;
-    auto load_tile = [&](int t, int buf) {
-        const uint32_t dst = sk_u + buf * (128 * kRowBytes);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int c = tid + i * 128;
-            const int r = c >> 4, ch = c & 15;
-            cp_async16(dst + tile_off(r, ch), kbase + (int64_t)(t * 128 + r) * k.sn + ch * 8, 16);
-        }
-    };
-    load_tile(t_begin, 0);
-    cp_async_commit();
-
-    const int words_per_row = N / 32;
-    for (int t = t_begin; t < t_end; ++t) {
-        const int buf = (t - t_begin) & 1;
-        if (t + 1 < t_end) {
-            load_tile(t + 1, buf ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-
-        // B fragments of this warp's 32 columns: [kstep][ntile][2]
-        uint32_t bfr[8][4][2];
-        const uint32_t kt = sk_u + buf * (128 * kRowBytes);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-#pragma unroll
-            for (int np = 0; np < 2; ++np) {
-                const int row = warp * 32 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
-                const int ch = ks * 2 + ((lane >> 3) & 1);
-                ldmatrix_x4(kt + tile_off(row, ch), bfr[ks][np * 2][0], bfr[ks][np * 2][1], bfr[ks][np * 2 + 1][0],
-                            bfr[ks][np * 2 + 1][1]);
-            }
-
-        for (int g = 0; g < Hg; ++g) {
-            uint32_t word = 0;
-            const int h = kvh * Hg + g;
-            for (int mt = 0; mt < step / 16; ++mt) {
-                float acc[4][4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-                const int arow0 = g * step + mt * 16;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    uint32_t a[4];
-                    const int row = arow0 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                    const int ch = ks * 2 + (lane >> 4);
-                    ldmatrix_x4(sq_u + tile_off(row, ch), a[0], a[1], a[2], a[3]);
-#pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) mma_bf16_16816(acc[nt], a, bfr[ks][nt][0], bfr[ks][nt][1]);
-                }
-                const int64_t prow = (int64_t)(z * H + h) * prow_per_head + b * step + mt * 16 + (lane >> 2);
-                const float a0 = apool[prow], a1 = apool[prow + 8];
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float sc = bf16_round(__fmul_rn(acc[nt][j], qk_scale));
-                        const bool hit = __fadd_rn(sc, diff) >= ((j < 2) ? a0 : a1);
-                        if (hit) word |= 1u << (nt * 8 + (lane & 3) * 2 + (j & 1));
-                    }
-            }
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) word |= __shfl_xor_sync(0xffffffffu, word, off);
-            if (lane == 0)
-                bitmap[((int64_t)(z * H + h) * NB + b) * words_per_row + t * 4 + warp] = word;
-        }
-        __syncthreads();
-    }
-}
-
-// ---------------------------------------------------------------------------
 // compact_kernel: grid (NB, H, B), 256 threads.  Turns the bitmap row of one
 // (head, big block) into an ascending id list and its count.
 // ---------------------------------------------------------------------------
@@ -206,7 +87,7 @@ __global__ void __launch_bounds__(256) compact_kernel(const uint32_t* __restrict
     __syncthreads();
     for (int c0 = 0; c0 < nwords; c0 += 256) {
         const int wi = c0 + tid;
-        uint32_t w = (wi < nwords) ? row[w0 + wi] : 0u;
+        const uint32_t w = (wi < nwords) ? row[w0 + wi] : 0u;
         const int cnt = __popc(w);
         int incl = cnt;
 #pragma unroll
@@ -223,12 +104,16 @@ __global__ void __launch_bounds__(256) compact_kernel(const uint32_t* __restrict
             if (i < warp) wbase += s;
             total += s;
         }
-        int pos = base_s + wbase + incl - cnt;
-        const int col0 = (w0 + wi) * 32;
-        while (w) {
-            const int bit = __ffs(w) - 1;
-            dst[pos++] = col0 + bit;
-            w &= w - 1;
+        // the warp writes its 32 words one after the other: lane i stores bit i of the word,
+        // so the ids of a word go out as one contiguous segment
+        const int excl = base_s + wbase + incl - cnt;
+        const uint32_t lt_mask = (1u << lane) - 1u;
+#pragma unroll 4
+        for (int k = 0; k < 32; ++k) {
+            const uint32_t wk = __shfl_sync(0xffffffffu, w, k);
+            const int ok_ = __shfl_sync(0xffffffffu, excl, k);
+            if (wk == 0u) continue;
+            if ((wk >> lane) & 1u) dst[ok_ + __popc(wk & lt_mask)] = (w0 + c0 + warp * 32 + k) * 32 + lane;
         }
         __syncthreads();
         if (tid == 0) base_s += total;
