@@ -16,8 +16,9 @@ EXPORTS = [
     "aa_workspace_bytes", "aa_workspace_layout", "aa_id_row_offset", "aa_forward",
     "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
-    "aa_launches_per_forward", "aa_step2_stripes_static",
+    "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
 ]
+MAX_PEERS = 8
 STATIC_SCRATCH_BYTES = 8 << 20
 
 
@@ -55,6 +56,10 @@ class AAStripesStaticArgs(ctypes.Structure):
     ]
 
 
+class AAPush(ctypes.Structure):
+    _fields_ = [("n_peers", ctypes.c_int32), ("out", ctypes.c_void_p * MAX_PEERS)]
+
+
 _lib = None
 
 
@@ -78,6 +83,8 @@ def load():
         getattr(lib, name).restype = ctypes.c_int
     lib.aa_step2_stripes_static.argtypes = [ctypes.POINTER(AAStripesStaticArgs), ctypes.c_void_p]
     lib.aa_step2_stripes_static.restype = ctypes.c_int
+    lib.aa_step3_sparse_push.argtypes = [P, ctypes.POINTER(AAPush), ctypes.c_void_p]
+    lib.aa_step3_sparse_push.restype = ctypes.c_int
     lib.aa_total_selected.argtypes = [P, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
     lib.aa_strerror.argtypes = [ctypes.c_int]
     lib.aa_strerror.restype = ctypes.c_char_p

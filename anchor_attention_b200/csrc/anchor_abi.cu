@@ -196,7 +196,8 @@ int make_gather_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, i
 }
 
 template <int MODE>
-int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st) {
+int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st,
+                     const aa_push_t* push = nullptr) {
     static thread_local int configured_dev[2] = {-1, -1};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -210,6 +211,12 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     aa::tc::TcArgs ta;
     ta.a = attend_args(p, lay);
     ta.status = ws_ptr<int32_t>(p, lay.status_off);
+    ta.n_peers = 0;
+    for (int i = 0; i < aa::tc::kMaxPeers; ++i) ta.peers[i] = nullptr;
+    if (push) {
+        ta.n_peers = push->n_peers;
+        for (int i = 0; i < push->n_peers; ++i) ta.peers[i] = static_cast<__nv_bfloat16*>(push->out[i]);
+    }
     CUtensorMap kmap, vmap;
     int rc = make_kv_map(&kmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.kpos_n,
                          &ta.kpos_h, &ta.kpos_b);
@@ -386,6 +393,21 @@ int aa_step3_sparse(const aa_params_t* p, void* stream) {
     int rc = check_full(p, &lay);
     if (rc) return rc;
     return launch_attend<aa::kStripe>(p, lay, static_cast<cudaStream_t>(stream));
+}
+
+int aa_step3_sparse_push(const aa_params_t* p, const aa_push_t* push, void* stream) {
+    if (!push) return AA_ERR_NULL;
+    if (push->n_peers < 1 || push->n_peers > AA_MAX_PEERS) return AA_ERR_SHAPE;
+    for (int i = 0; i < push->n_peers; ++i) {
+        if (!push->out[i]) return AA_ERR_NULL;
+        if ((uintptr_t)push->out[i] & 15) return AA_ERR_STRIDE;
+    }
+    aa_params_t q = *p;
+    q.out = push->out[0];                      // the argument checks want a non-NULL output
+    aa_workspace_layout_t lay;
+    int rc = check_full(&q, &lay);
+    if (rc) return rc;
+    return launch_attend_tc<aa::kStripe>(&q, lay, static_cast<cudaStream_t>(stream), push);
 }
 
 int aa_forward(const aa_params_t* p, void* stream) {

@@ -68,11 +68,15 @@ constexpr int kSmemTotal = kSmemQ + kSmemRing + kSmemBars + 1024;   // + slack t
 constexpr float kRescaleThreshold = 8.0f;
 constexpr uint32_t kTmemCols = 512;
 
+constexpr int kMaxPeers = 8;
+
 struct TcArgs {
     AttendArgs a;
     int kpos_n, kpos_h, kpos_b;      // which tensor-map coordinate (1..3 -> 0..2) carries n / head / batch
     int vpos_n, vpos_h, vpos_b;
     int k_gather, v_gather;          // 1: the 2-D row-gather tensor map of K / V is usable
+    int n_peers;                     // step 3 only: > 0 -> write the output to peers[0 .. n_peers) instead of a.out
+    __nv_bfloat16* peers[kMaxPeers]; // same element offsets and strides as a.out; may be other GPUs' memory
     int32_t* status;
 };
 
@@ -396,7 +400,8 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                                                      __uint_as_float(v[4 * i + 3]) * sc);
                 }
             } else {
-                __nv_bfloat16* orow = a.out + z * a.osb + h * a.osh + (int64_t)row_g * a.osn;
+                const int64_t ooff = z * a.osb + h * a.osh + (int64_t)row_g * a.osn;
+                __nv_bfloat16* orow = a.out + ooff;
                 const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -421,7 +426,14 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                         o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
                         o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
                         o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o4;
+                        if (ta.n_peers == 0) {
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o4;
+                        } else {
+                            // head-parallel runs: the row goes straight into every rank's copy of the
+                            // assembled output (plain 16-byte stores over NVLink, no collective afterwards)
+                            for (int pr = 0; pr < ta.n_peers; ++pr)
+                                *reinterpret_cast<uint4*>(ta.peers[pr] + ooff + c * 32 + i * 8) = o4;
+                        }
                     }
                 }
             }

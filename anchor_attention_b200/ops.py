@@ -115,6 +115,20 @@ class AnchorAttnCall:
         self._call(self._lib.aa_step3_sparse)
         return self.out
 
+    def step3_push(self, peer_ptrs):
+        """Step 3 that stores every output row to each address in ``peer_ptrs`` (device
+        pointers with this call's output strides; may be other GPUs' memory) instead of
+        ``self.out``.  Used by the head-parallel wrapper."""
+        push = _lib.AAPush()
+        push.n_peers = len(peer_ptrs)
+        for i, ptr in enumerate(peer_ptrs):
+            push.out[i] = ptr
+        with torch.cuda.device(self.Q.device):
+            rc = self._lib.aa_step3_sparse_push(ctypes.byref(self.params), ctypes.byref(push),
+                                                ctypes.c_void_p(self.stream.cuda_stream))
+        if rc != _lib.AA_OK:
+            raise RuntimeError(f"anchor_attn: {_lib.error_text(rc)}")
+
     def check_status(self):
         self._call(self._lib.aa_check_status)
 

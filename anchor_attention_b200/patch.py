@@ -87,31 +87,37 @@ def _dense_causal(query, key, value, scaling, q_offset):
 
 _head_parallel_group = None
 _head_parallel_on = False
+_head_parallel_exchange = "push"
+_head_parallel_ops = {}
 
 
-def set_head_parallel_group(group):
+def set_head_parallel_group(group, exchange: str = "push"):
     """Run the sparse part of every patched attention layer head-parallel over the
     ranks of ``group`` (a torch.distributed process group; ``None`` switches it off):
-    each rank computes its KV-head groups and one all-gather assembles all heads.
-    Every rank must call the model with the same inputs."""
-    global _head_parallel_group, _head_parallel_on
+    each rank computes its KV-head groups and the head outputs reach every rank either
+    by step 3 storing them into all ranks' output copies ("push") or by one NCCL
+    all-gather ("all_gather").  Every rank must call the model with the same inputs."""
+    global _head_parallel_group, _head_parallel_on, _head_parallel_exchange
     _head_parallel_group = group
     _head_parallel_on = group is not None
+    _head_parallel_exchange = exchange
+    _head_parallel_ops.clear()
 
 
 def _head_parallel_anchor_attn(query, key, value, scaling, block, step, theta, _ratio):
     """anchor_attn on this rank's heads, then the all-gather; returns [B,H,N,D] (a view
     of token-major memory)."""
     import torch.distributed as dist
-    from .ops import AnchorAttnCall
-    from .parallel import gather_heads, head_partition
+    from .parallel import HeadShardedAnchorAttn, head_partition
     W, rank = dist.get_world_size(_head_parallel_group), dist.get_rank(_head_parallel_group)
     B, H, N, D = query.shape
     q_lo, q_hi, kv_lo, kv_hi = head_partition(H, key.shape[1], W, rank)
-    local = torch.empty((B, N, q_hi - q_lo, D), dtype=query.dtype, device=query.device)
-    AnchorAttnCall(query[:, q_lo:q_hi], key[:, kv_lo:kv_hi], value[:, kv_lo:kv_hi], scaling, block, step, theta,
-                   out=local.permute(0, 2, 1, 3)).run()
-    return gather_heads(local, _head_parallel_group).permute(0, 2, 1, 3)
+    key_ = (scaling, block, step, theta)
+    op = _head_parallel_ops.get(key_)
+    if op is None:
+        op = _head_parallel_ops[key_] = HeadShardedAnchorAttn(scaling, block, step, theta, _head_parallel_group,
+                                                              exchange=_head_parallel_exchange)
+    return op(query[:, q_lo:q_hi], key[:, kv_lo:kv_hi], value[:, kv_lo:kv_hi]).permute(0, 2, 1, 3)
 
 
 def anchor_attention_forward(module, query, key, value, attention_mask=None, scaling: Optional[float] = None,

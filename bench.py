@@ -7,8 +7,10 @@ Workload: one Llama-3.1-8B-shape attention layer (32 query / 8 KV heads, head
 size 128, bf16, causal, batch 1) at 131072 tokens on seeded synthetic tensors
 (N(0,1) entries, sink rows, 1 % stripe columns, RoPE at base 500000), block 128,
 step 16, theta 12.  With N > 1 GPUs the heads are partitioned by KV group across
-the ranks and the head outputs exchanged with one NCCL all-gather (strong
-scaling of the fixed layer).  Prints ONE JSON line on rank 0.
+the ranks (strong scaling of the fixed layer); every rank ends with all head
+outputs, either because step 3 stores its rows into every rank's output copy over
+NVLink while it computes (default) or through one NCCL all-gather
+(``--exchange all_gather``).  Prints ONE JSON line on rank 0.
 
 ``--impl reference`` times the CPU restatement of the reference operator on the
 host cores on a bounded sample of the same workload and extrapolates to the
@@ -178,7 +180,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from anchor_attention_b200 import AnchorAttnCall, launches_per_forward
-    from anchor_attention_b200.parallel import gather_heads, head_partition
+    from anchor_attention_b200.parallel import HeadShardedAnchorAttn, PushedOutput, gather_heads, head_partition
     from anchor_attention_b200.synthetic import make_inputs
 
     if not torch.cuda.is_available():
@@ -196,19 +198,35 @@ def run_ours(args):
     q_lo, q_hi, kv_lo, kv_hi = head_partition(H, HKV, W, rank)
     h = q_hi - q_lo
     Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, heads=(q_lo, q_hi, kv_lo, kv_hi))
-    out_local = torch.empty((1, N, h, D), dtype=torch.bfloat16, device=dev)        # token-major
-    gathered = torch.empty((W, 1, N, h, D), dtype=torch.bfloat16, device=dev) if W > 1 else None
-    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA, out=out_local.permute(0, 2, 1, 3))
+    push = W > 1 and args.exchange == "push"
+    if push:
+        # every rank's copy of the assembled [1,N,H,D] output lives in symmetric memory; step 3
+        # stores this rank's heads into all copies, a barrier replaces the all-gather
+        pushed = PushedOutput(1, N, H, D, torch.bfloat16, dev)
+        out_view = pushed.bufs[0][:, :, q_lo:q_hi].permute(0, 2, 1, 3)
+        head_off = q_lo * D * 2
+        gathered = None
+    else:
+        out_local = torch.empty((1, N, h, D), dtype=torch.bfloat16, device=dev)        # token-major
+        out_view = out_local.permute(0, 2, 1, 3)
+        gathered = torch.empty((W, 1, N, h, D), dtype=torch.bfloat16, device=dev) if W > 1 else None
+    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA, out=out_view)
 
     def step(ev=None):
         call.step1()
         call.step2()
         if ev is not None:
             ev[0].record()
-        call.step3()
+        if push:
+            _, ptrs, handle = pushed.next()
+            call.step3_push([p + head_off for p in ptrs])
+        else:
+            call.step3()
         if ev is not None:
             ev[1].record()
-        if W > 1:
+        if push:
+            handle.barrier(channel=0)
+        elif W > 1:
             gather_heads(out_local, None, gathered)
 
     def barrier():
@@ -241,12 +259,16 @@ def run_ours(args):
     hout = torch.empty((1, h, N, D), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(1, min(args.steps, 3))
 
+    sharded = HeadShardedAnchorAttn(None, BLOCK, STEP, THETA, exchange=args.exchange) if W > 1 else None
+
     def e2e_step():
         dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-        o = anchor_attn(dq, dk, dv, None, BLOCK, STEP, THETA, return_computational_ratio=False)
         if W > 1:
-            gather_heads(o.transpose(1, 2).contiguous(), None, gathered)
-        hout.copy_(o, non_blocking=True)
+            full = sharded(dq, dk, dv)                                   # [1,N,H,D] on every rank
+            hout.copy_(full[:, :, q_lo:q_hi].permute(0, 2, 1, 3), non_blocking=True)
+        else:
+            o = anchor_attn(dq, dk, dv, None, BLOCK, STEP, THETA, return_computational_ratio=False)
+            hout.copy_(o, non_blocking=True)
 
     e2e_step()
     barrier()
@@ -284,7 +306,9 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"anchor_attn layer, seq {N}, {H}q/{HKV}kv heads, head_dim {D}, block {BLOCK}, "
                                    f"step {STEP}, theta {THETA}",
-                       "parallelism": f"heads by KV group over {W} GPU(s), one all-gather" if W > 1 else "single GPU",
+                       "parallelism": (f"heads by KV group over {W} GPU(s), " +
+                                       ("step 3 stores its rows into every rank's output over NVLink, one barrier"
+                                        if push else "one NCCL all-gather")) if W > 1 else "single GPU",
                        "l2": "inputs_exceed_l2", "density": counts_all / cap if cap else 0.0,
                        "selected_columns": counts_all},
             "algorithmic_tflop": {"step1": f1 / 1e12, "step2": f2 / 1e12, "step3": f3 / 1e12},
@@ -314,6 +338,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=131072)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="push", choices=["push", "all_gather"],
+                    help="how the head outputs reach every rank when N > 1")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -117,6 +117,20 @@ int aa_step2_stripes(const aa_params_t *p, void *stream);
  * _triton_stripe_sparse_attn_fwd_kernel_step3 (anchor_attn_v4.py:246-268). */
 int aa_step3_sparse(const aa_params_t *p, void *stream);
 
+/* Step 3 for head-parallel runs: identical to aa_step3_sparse, except that every output
+ * row is stored to push->out[0 .. n_peers) instead of p->out -- same element offsets and
+ * strides (p->o_stride_*) in each.  The pointers may be peer-mapped memory of other GPUs
+ * of the node (symmetric or IPC-opened buffers): each rank then writes its heads into every
+ * rank's copy of the assembled [B,N,H,D] output while it computes, and no all-gather
+ * follows; the ranks only need a barrier before they read their copy.  p->out is ignored.
+ * (No counterpart in the reference, which is single-GPU: test_hf.py:126.) */
+#define AA_MAX_PEERS 8
+typedef struct aa_push {
+    int32_t n_peers;
+    void   *out[AA_MAX_PEERS];
+} aa_push_t;
+int aa_step3_sparse_push(const aa_params_t *p, const aa_push_t *push, void *stream);
+
 /* Reads the device status word (synchronises the stream first).  Returns AA_OK
  * or AA_ERR_DEVICE_TIMEOUT / AA_ERR_CUDA. */
 int aa_check_status(const aa_params_t *p, void *stream);

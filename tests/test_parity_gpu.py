@@ -213,3 +213,22 @@ def test_full_size_sampled_blocks_and_properties(lib):
         err = (outc[0, h, rows] - oout[rows]).abs()
         assert err.max() <= OUT_MAX_ABS and err.mean() <= OUT_MEAN_ABS
         assert int(counts[0, h, b]) == oids[b].numel()
+
+
+def test_step3_push_writes_every_copy(lib):
+    """The push variant of step 3 (used head-parallel) stores the same bits as step 3 into
+    each of the given output copies; here both copies are local buffers."""
+    from anchor_attention_b200 import AnchorAttnCall
+    Q, K, V = (t.cuda() for t in make_inputs(6144, 4, 2, seed=41, rope=True, q_shift=0.5))
+    copies = torch.zeros((2, 1, 6144, 6, 128), dtype=torch.bfloat16, device="cuda")    # two [B,N,H+2,D] buffers
+    view = copies[0][:, :, 1:5].permute(0, 2, 1, 3)                                    # heads 1..4 of copy 0
+    call = AnchorAttnCall(Q, K, V, None, 128, 16, 10.0, out=view)
+    call.step1()
+    call.step2()
+    head_off = 1 * 128 * 2
+    call.step3_push([copies[0].data_ptr() + head_off, copies[1].data_ptr() + head_off])
+    call.check_status()
+    want = AnchorAttnCall(Q, K, V, None, 128, 16, 10.0).run().transpose(1, 2)
+    for c in range(2):
+        assert torch.equal(copies[c][:, :, 1:5], want)
+        assert not copies[c][:, :, 0].any() and not copies[c][:, :, 5].any()
