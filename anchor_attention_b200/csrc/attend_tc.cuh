@@ -382,8 +382,8 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             tcgen05_fence_after();
         }
-        if (ok) {
-            if (MODE == kWindow) {
+        if (MODE == kWindow) {
+            if (ok) {
                 const float sc = fast_exp2(m_ref - m_true);
                 a.M[srow] = m_true;
                 a.L[srow] = l * sc;
@@ -399,9 +399,15 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                                                      __uint_as_float(v[4 * i + 2]) * sc,
                                                      __uint_as_float(v[4 * i + 3]) * sc);
                 }
-            } else {
-                const int64_t ooff = z * a.osb + h * a.osh + (int64_t)row_g * a.osn;
-                __nv_bfloat16* orow = a.out + ooff;
+            }
+        } else {
+            // The 128 rows of the tile are staged in shared memory (the tile's query buffer, which
+            // no MMA reads any more) and then written out as whole 256-byte rows by consecutive
+            // threads: coalesced stores, which matters most when the destination is another GPU.
+            // All 128 threads of the tile get here; they first agree that none of them gave up.
+            const bool all_ok = bar_and(1 + j, 128, ok);
+            if (all_ok) {
+                uint8_t* stage = smem + j * kTileBytes;
                 const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -426,14 +432,25 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                         o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
                         o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
                         o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
-                        if (ta.n_peers == 0) {
-                            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o4;
-                        } else {
-                            // head-parallel runs: the row goes straight into every rank's copy of the
-                            // assembled output (plain 16-byte stores over NVLink, no collective afterwards)
-                            for (int pr = 0; pr < ta.n_peers; ++pr)
-                                *reinterpret_cast<uint4*>(ta.peers[pr] + ooff + c * 32 + i * 8) = o4;
-                        }
+                        // row r, 16-byte chunk c*4+i, stored at chunk slot (chunk ^ (r & 7)): conflict-free
+                        *reinterpret_cast<uint4*>(stage + r * kRowBytes + (((c * 4 + i) ^ (r & 7)) << 4)) = o4;
+                    }
+                }
+                bar_sync(1 + j, 128);
+                const int64_t tile_off = z * a.osb + h * a.osh + (int64_t)qb * kTile * a.osn;
+                const int ch = r & 15;
+#pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                    const int row = it * 8 + (r >> 4);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
+                    const int64_t off = tile_off + (int64_t)row * a.osn + ch * 8;
+                    if (ta.n_peers == 0) {
+                        *reinterpret_cast<uint4*>(a.out + off) = val;
+                    } else {
+                        // head-parallel runs: the rows go straight into every rank's copy of the
+                        // assembled output (16-byte stores, a row per 16 threads, over NVLink);
+                        // no collective follows
+                        for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint4*>(ta.peers[pr] + off) = val;
                     }
                 }
             }
