@@ -161,8 +161,8 @@ int aa_total_selected(const aa_params_t *p, void *stream, int64_t *total);
  *
  * - Problems whose intermediates exceed the array are refused with
  *   AA_ERR_TOO_LARGE; nothing is launched.  The need is
- *   B*H*(N/128)*(256+4) + B*H*NB*(N/32)*4 bytes plus alignment padding, e.g.
- *   4.1 MiB for B*H = 32, N = 32768.
+ *   B*H*(N/128)*(256+4) + B*H*NB*(N/32)*4 + 256 bytes plus alignment padding,
+ *   e.g. 4.1 MiB for B*H = 32, N = 32768.
  * - It calls no cudaMalloc / cudaFree and no allocating library routine.
  * - The first call on a device looks up the array's device address (once per
  *   device, with that device current); make that first call before starting
