@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["anchor_attn", "AnchorAttnCall", "launches_per_forward"]
+__all__ = ["anchor_attn", "anchor_attn_without_anchor", "AnchorAttnCall", "launches_per_forward"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -215,6 +215,17 @@ def anchor_attn(Q, K, V,
     if return_computational_ratio:
         return out, call.ratio()
     return out
+
+
+def anchor_attn_without_anchor(Q, K, V,
+                               sm_scale: float = None,
+                               block_size: int = 128,
+                               step: int = 16,
+                               difference: float = 12):
+    """The reference's second entry point (anchor_attn/src/ops/anchor_attn_v4.py:275-289,
+    171-224): the same three steps with the same arithmetic as ``anchor_attn``; it always
+    returns ``(out, sparsity_ratio)``."""
+    return anchor_attn(Q, K, V, sm_scale, block_size, step, difference, return_computational_ratio=True)
 
 
 def launches_per_forward() -> int:

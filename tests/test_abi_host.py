@@ -96,3 +96,31 @@ def test_python_entry_point_refuses_cpu_tensors(lib):
     q = torch.zeros(1, 1, 2048, 128, dtype=torch.bfloat16)
     with pytest.raises(AssertionError, match="no CPU path"):
         anchor_attn(q, q, q)
+
+
+def test_push_entry_point_validates_its_arguments(lib):
+    p = _params()
+    p.q = p.k = p.v = p.out = 4096
+    for name in ("q", "k", "v", "o"):
+        setattr(p, f"{name}_stride_n", 128)
+    push = _lib.AAPush()
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), None, None) == -1          # no push block
+    push.n_peers = 0
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
+    push.n_peers = _lib.MAX_PEERS + 1
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
+    push.n_peers = 2
+    push.out[0] = 4096
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -1          # out[1] is NULL
+    push.out[1] = 4100
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -8          # not 16-byte aligned
+    push.out[1] = 8192
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -7          # no workspace
+
+
+def test_without_anchor_alias_exists():
+    from anchor_attention_b200 import anchor_attn_without_anchor
+    import inspect
+    sig = inspect.signature(anchor_attn_without_anchor)
+    assert list(sig.parameters) == ["Q", "K", "V", "sm_scale", "block_size", "step", "difference"]
+    assert sig.parameters["difference"].default == 12 and sig.parameters["block_size"].default == 128
