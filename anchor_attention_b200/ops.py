@@ -19,7 +19,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["anchor_attn", "anchor_attn_without_anchor", "AnchorAttnCall", "launches_per_forward"]
+__all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
+           "launches_per_forward"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 
@@ -226,6 +227,66 @@ def anchor_attn_without_anchor(Q, K, V,
     171-224): the same three steps with the same arithmetic as ``anchor_attn``; it always
     returns ``(out, sparsity_ratio)``."""
     return anchor_attn(Q, K, V, sm_scale, block_size, step, difference, return_computational_ratio=True)
+
+
+def anchor_attn_host(Q, K, V, out=None,
+                     sm_scale: float = None,
+                     block_size: int = 128,
+                     step: int = 16,
+                     difference: float = 12,
+                     device=None):
+    """``anchor_attn`` for tensors that live in (pinned) host memory: Q [B,H,N,D], K/V
+    [B,Hkv,N,D] bf16 on the CPU in, ``out`` [B,H,N,D] on the CPU out (allocated pinned if
+    not given).  The KV-head groups are independent, so they are streamed: while group g
+    computes on the device, group g+1 is copied in and the result of group g-1 is copied
+    out, each on its own CUDA stream.  The call returns once ``out`` is complete.
+    Same arithmetic, head by head, as ``anchor_attn`` on device tensors."""
+    assert not Q.is_cuda and not K.is_cuda and not V.is_cuda, "anchor_attn_host takes host tensors"
+    B, H, N, D = Q.shape
+    Hkv = K.shape[1]
+    assert H % Hkv == 0, f"{Hkv} KV heads do not divide {H} query heads"
+    Hg = H // Hkv
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    if out is None:
+        out = torch.empty((B, H, N, D), dtype=Q.dtype).pin_memory()
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dq = [torch.empty((B, Hg, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
+    dk = [torch.empty((B, 1, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
+    dv = [torch.empty((B, 1, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
+    do = [torch.empty((B, Hg, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
+    loaded = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
+
+    def copy_in(g):
+        i = g & 1
+        with torch.cuda.stream(s_in):
+            if g >= 2:
+                s_in.wait_event(computed[i])          # the buffers' previous user (group g-2) is done
+            dq[i].copy_(Q[:, g * Hg:(g + 1) * Hg], non_blocking=True)
+            dk[i].copy_(K[:, g:g + 1], non_blocking=True)
+            dv[i].copy_(V[:, g:g + 1], non_blocking=True)
+            loaded[i].record(s_in)
+
+    s_in.wait_stream(main)
+    copy_in(0)
+    for g in range(Hkv):
+        i = g & 1
+        if g + 1 < Hkv:
+            copy_in(g + 1)
+        main.wait_event(loaded[i])
+        if g >= 2:
+            main.wait_event(drained[i])               # the output buffer has been copied out
+        AnchorAttnCall(dq[i], dk[i], dv[i], sm_scale, block_size, step, difference, out=do[i]).run()
+        computed[i].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(computed[i])
+            out[:, g * Hg:(g + 1) * Hg].copy_(do[i], non_blocking=True)
+            drained[i].record(s_out)
+    main.wait_stream(s_out)
+    main.synchronize()
+    return out
 
 
 def launches_per_forward() -> int:

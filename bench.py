@@ -199,10 +199,22 @@ def run_ours(args):
     h = q_hi - q_lo
     Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, heads=(q_lo, q_hi, kv_lo, kv_hi))
     push = W > 1 and args.exchange == "push"
+    exchange_note = ""
     if push:
         # every rank's copy of the assembled [1,N,H,D] output lives in symmetric memory; step 3
         # stores this rank's heads into all copies, a barrier replaces the all-gather
-        pushed = PushedOutput(1, N, H, D, torch.bfloat16, dev)
+        try:
+            pushed = PushedOutput(1, N, H, D, torch.bfloat16, dev)
+            failed = 0
+        except Exception as e:      # symmetric memory could not be set up on this machine
+            failed, exchange_note = 1, f"symmetric memory unavailable ({type(e).__name__}), used the all-gather"
+        flag = torch.tensor([failed], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            push = False
+            args.exchange = "all_gather"
+            exchange_note = exchange_note or "symmetric memory unavailable on another rank, used the all-gather"
+    if push:
         out_view = pushed.bufs[0][:, :, q_lo:q_hi].permute(0, 2, 1, 3)
         head_off = q_lo * D * 2
         gathered = None
@@ -254,7 +266,7 @@ def run_ours(args):
     counts_total = int(call.counts.sum())
 
     # ---- end to end through the public entry point, host buffers in, host result out
-    from anchor_attention_b200 import anchor_attn
+    from anchor_attention_b200 import anchor_attn_host
     hq, hk, hv = (t.cpu().pin_memory() for t in (Q, K, V))
     hout = torch.empty((1, h, N, D), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(1, min(args.steps, 3))
@@ -262,13 +274,14 @@ def run_ours(args):
     sharded = HeadShardedAnchorAttn(None, BLOCK, STEP, THETA, exchange=args.exchange) if W > 1 else None
 
     def e2e_step():
+        if W == 1:
+            # host buffers in, host buffer out; the KV-head groups are streamed so that the copies
+            # of one group overlap the computation of another
+            anchor_attn_host(hq, hk, hv, hout, None, BLOCK, STEP, THETA, device=dev)
+            return
         dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-        if W > 1:
-            full = sharded(dq, dk, dv)                                   # [1,N,H,D] on every rank
-            hout.copy_(full[:, :, q_lo:q_hi].permute(0, 2, 1, 3), non_blocking=True)
-        else:
-            o = anchor_attn(dq, dk, dv, None, BLOCK, STEP, THETA, return_computational_ratio=False)
-            hout.copy_(o, non_blocking=True)
+        full = sharded(dq, dk, dv)                                       # [1,N,H,D] on every rank
+        hout.copy_(full[:, :, q_lo:q_hi].permute(0, 2, 1, 3), non_blocking=True)
 
     e2e_step()
     barrier()
@@ -309,6 +322,7 @@ def run_ours(args):
                        "parallelism": (f"heads by KV group over {W} GPU(s), " +
                                        ("step 3 stores its rows into every rank's output over NVLink, one barrier"
                                         if push else "one NCCL all-gather")) if W > 1 else "single GPU",
+                       "exchange_note": exchange_note,
                        "l2": "inputs_exceed_l2", "density": counts_all / cap if cap else 0.0,
                        "selected_columns": counts_all},
             "algorithmic_tflop": {"step1": f1 / 1e12, "step2": f2 / 1e12, "step3": f3 / 1e12},

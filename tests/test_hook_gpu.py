@@ -80,3 +80,13 @@ def test_recall_harness_against_dense_attention(lib):
     assert dens[0] <= dens[1] <= dens[2] and dens[2] > 0.5
     for r in rows:
         assert 0.0 <= r["recall@0.005"] <= r["recall@0.01"] <= 1.0
+
+
+def test_host_buffer_entry_point_matches_device_call(lib):
+    """anchor_attn_host streams the KV-head groups through the device (copy in, compute,
+    copy out overlapped); its result has the bits of the device-tensor call."""
+    from anchor_attention_b200 import anchor_attn, anchor_attn_host
+    Q, K, V = make_inputs(6144, 6, 3, seed=61, rope=True, q_shift=0.5)
+    want = anchor_attn(Q.cuda(), K.cuda(), V.cuda(), difference=10.0, return_computational_ratio=False).cpu()
+    got = anchor_attn_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), None, None, 128, 16, 10.0)
+    assert got.shape == want.shape and torch.equal(got, want)

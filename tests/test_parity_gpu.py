@@ -232,3 +232,33 @@ def test_step3_push_writes_every_copy(lib):
     for c in range(2):
         assert torch.equal(copies[c][:, :, 1:5], want)
         assert not copies[c][:, :, 0].any() and not copies[c][:, :, 5].any()
+
+
+def test_batch_fused_qkv_and_padded_heads(lib):
+    """Batch of two; Q/K/V as slices of one fused [B,N,(H+2*Hkv)*D] projection output; K/V
+    heads separated by padding (no 2-D tensor map covers them, so the gathers fall back to
+    cp.async only).  All give the bits of the plain contiguous call, batch by batch."""
+    from anchor_attention_b200 import anchor_attn
+    N, H, Hkv, theta = 6144, 4, 2, 10.0
+    parts = [make_inputs(N, H, Hkv, seed=s, rope=True, q_shift=0.5) for s in (51, 52)]
+    Q, K, V = (torch.cat([p[i] for p in parts], dim=0).cuda() for i in range(3))
+    per_batch = [anchor_attn(*(t.cuda() for t in p), difference=theta, return_computational_ratio=False)
+                 for p in parts]
+    base = torch.cat(per_batch, dim=0)
+    assert torch.equal(anchor_attn(Q, K, V, difference=theta, return_computational_ratio=False), base)
+    # fused projection output, token-major: [B, N, (H + 2 Hkv) * D]
+    fused = torch.cat([Q.transpose(1, 2).reshape(2, N, H * 128), K.transpose(1, 2).reshape(2, N, Hkv * 128),
+                       V.transpose(1, 2).reshape(2, N, Hkv * 128)], dim=2).contiguous()
+    Qf = fused[:, :, :H * 128].view(2, N, H, 128).transpose(1, 2)
+    Kf = fused[:, :, H * 128:(H + Hkv) * 128].view(2, N, Hkv, 128).transpose(1, 2)
+    Vf = fused[:, :, (H + Hkv) * 128:].view(2, N, Hkv, 128).transpose(1, 2)
+    assert torch.equal(anchor_attn(Qf, Kf, Vf, difference=theta, return_computational_ratio=False), base)
+    # heads padded apart by 8 elements: head stride N*128 + 8
+    def padded(x):
+        B, h, n, d = x.shape
+        buf = torch.zeros((B, h, n * d + 8), dtype=x.dtype, device=x.device)
+        buf[:, :, :n * d] = x.reshape(B, h, n * d)
+        return buf[:, :, :n * d].view(B, h, n, d)
+    Kp, Vp = padded(K), padded(V)
+    assert Kp.stride(1) == N * 128 + 8
+    assert torch.equal(anchor_attn(Q, Kp, Vp, difference=theta, return_computational_ratio=False), base)
