@@ -135,6 +135,268 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, u
     tma_load_4d(dst + kSlabBytes, map, bar, 64, c0, c1, c2);
 }
 
+// What the softmax warps need to know about their CTA: where the tiles and barriers are.
+// q_full / p_ready / p_ready2 are arrived on (shared::cluster addresses when CLUSTER, so that
+// they may belong to the leader CTA of a pair), s_full / o_done are waited on (always local).
+struct SoftmaxCtx {
+    uint8_t* smem;
+    uint32_t tmem_base;
+    volatile int* abort_flag;
+    uint32_t q_full[2], s_full[2], p_ready[2], p_ready2[2], o_done[2];
+    int pair, z, h, hz, ntiles, n_init, local_start, count;
+};
+
+template <bool CLUSTER>
+__device__ __forceinline__ void arrive_on(uint32_t bar) {
+    if (CLUSTER)
+        mbar_arrive_cluster(bar);
+    else
+        mbar_arrive(bar);
+}
+
+// The softmax role of warps 0-7 (see the file header): thread r of tile j owns query row r.
+template <int MODE, bool CLUSTER>
+__device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx& cx, int tid) {
+    const AttendArgs& a = ta.a;
+    const int warp = tid >> 5;
+    uint8_t* smem = cx.smem;
+    const uint32_t tmem_base = cx.tmem_base;
+    volatile int* abort_flag = cx.abort_flag;
+    const int pair = cx.pair, z = cx.z, h = cx.h, hz = cx.hz;
+    const int ntiles = cx.ntiles, n_init = cx.n_init, local_start = cx.local_start, count = cx.count;
+    (void)n_init; (void)local_start; (void)count;
+    const int j = warp >> 2;
+    const uint32_t q_full_j = cx.q_full[j], s_full_j = cx.s_full[j], o_done_j = cx.o_done[j];
+    const uint32_t p_ready_j = cx.p_ready[j], p_ready2_j = cx.p_ready2[j];
+    const int r = tid & 127;
+    const int qb = 2 * pair + j;
+    const int row_g = qb * kTile + r;
+    const int64_t srow = (int64_t)hz * a.N + row_g;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + (uint32_t)j * 128u;
+    const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)j * 128u;
+
+    // Q tile: load, scale, round, store in the K-major 128B-swizzled layout the MMA reads
+    {
+        const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
+        const float c1 = bf16_round(a.sm_scale), c2 = bf16_round(kLog2e);
+        uint8_t* qs = smem + j * kTileBytes;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+            const int id = r + 128 * i;
+            const int rr = id >> 4, ch = id & 15;
+            uint4 raw = *reinterpret_cast<const uint4*>(qbase + (int64_t)rr * a.q.sn + ch * 8);
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 f = __bfloat1622float2(p2[e]);
+                if (MODE == kWindow) {
+                    f.x = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.x, c1)), c2));
+                    f.y = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.y, c1)), c2));
+                } else {
+                    f.x = __fmul_rn(__fmul_rn(f.x, a.sm_scale), kLog2e);
+                    f.y = __fmul_rn(__fmul_rn(f.y, a.sm_scale), kLog2e);
+                }
+                p2[e] = __floats2bfloat162_rn(f.x, f.y);
+            }
+            *reinterpret_cast<uint4*>(qs + sw_off(rr, ch)) = raw;
+        }
+        fence_proxy_async();
+        arrive_on<CLUSTER>(q_full_j);
+    }
+
+    float m_true, m_ref, l;
+    if (MODE == kStripe) {
+        m_true = m_ref = a.M[srow];
+        l = a.L[srow];
+        if (ntiles > 0) {
+            const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 x = src[c * 8 + i];
+                    v[4 * i] = __float_as_uint(x.x);
+                    v[4 * i + 1] = __float_as_uint(x.y);
+                    v[4 * i + 2] = __float_as_uint(x.z);
+                    v[4 * i + 3] = __float_as_uint(x.w);
+                }
+                tmem_st32(tO + c * 32, v);
+            }
+            tmem_wait_st();
+        }
+    } else {
+        m_true = m_ref = -INFINITY;
+        l = 0.f;
+    }
+
+    bool ok = true;
+    for (int t = 0; t < ntiles && ok; ++t) {
+        ok = mbar_wait(s_full_j, t & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
+        tmem_wait_ld();
+
+        if (MODE == kWindow) {
+            const int col0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
+            if (col0 + kTile - 1 > qb * kTile) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + c * 32 + i > row_g)
+                            sv[c][i] = __float_as_uint(__uint_as_float(sv[c][i]) + -1e6f);
+            }
+        } else {
+            const int valid = count - t * kTile;
+            if (valid < kTile) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i >= valid) sv[c][i] = __float_as_uint(-INFINITY);
+            }
+        }
+        {   // row maximum: four independent chains of three-input max
+            float mx[4] = {m_true, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2)
+                    mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+            m_true = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        }
+        // move the exponent reference only when some row of the warp needs it
+        if (__any_sync(0xffffffffu, m_true > m_ref + kRescaleThreshold)) {
+            const float alpha = fast_exp2(m_ref - m_true);
+            if (!(MODE == kWindow && t == 0)) {
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tO + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st32(tO + c * 32, v);
+                }
+            }
+            l *= alpha;
+            m_ref = m_true;
+        }
+        float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+        const float2 neg_ref = make_float2(-m_ref, -m_ref);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int e = c * 64 + 2 * i;
+                const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
+                                                        __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
+                // kPolyShare of every 4 element pairs take the polynomial on the FMA pipe,
+                // the others the MUFU unit: both pipes are busy
+                const float2 p = ((i & 3) < kPolyShare) ? exp2_poly2(d) : make_float2(fast_exp2(d.x), fast_exp2(d.y));
+                rs[i & 3] = __fadd2_rn(rs[i & 3], p);
+                pk[i] = pack_bf16x2(p.x, p.y);
+            }
+            tmem_st32(tS + c * 32, pk);
+            // the first 64 columns of P are enough for the first four k-steps of P V
+            if (kSplitP || c == 1) {
+                tmem_wait_st();
+                tcgen05_fence_before();
+                arrive_on<CLUSTER>((kSplitP && c == 1) ? p_ready2_j : p_ready_j);
+            }
+        }
+        const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
+        l += rsum.x + rsum.y;
+    }
+
+    // ---- epilogue ----
+    if (ok && ntiles > 0) {
+        ok = mbar_wait(o_done_j, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        tcgen05_fence_after();
+    }
+    if (MODE == kWindow) {
+        if (ok) {
+            const float sc = fast_exp2(m_ref - m_true);
+            a.M[srow] = m_true;
+            a.L[srow] = l * sc;
+            float4* dst = reinterpret_cast<float4*>(a.Acc + srow * kD);
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tO + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    dst[c * 8 + i] = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
+                                                 __uint_as_float(v[4 * i + 2]) * sc,
+                                                 __uint_as_float(v[4 * i + 3]) * sc);
+            }
+        }
+    } else {
+        // The 128 rows of the tile are staged in shared memory (the tile's query buffer, which
+        // no MMA reads any more) and then written out as whole 256-byte rows by consecutive
+        // threads: coalesced stores, which matters most when the destination is another GPU.
+        // All 128 threads of the tile get here; they first agree that none of them gave up.
+        const bool all_ok = bar_and(1 + j, 128, ok);
+        if (all_ok) {
+            uint8_t* stage = smem + j * kTileBytes;
+            const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                if (ntiles > 0) {
+                    tmem_ld32(tO + c * 32, v);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 x = src[c * 8 + i];
+                        v[4 * i] = __float_as_uint(x.x);
+                        v[4 * i + 1] = __float_as_uint(x.y);
+                        v[4 * i + 2] = __float_as_uint(x.z);
+                        v[4 * i + 3] = __float_as_uint(x.w);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 o4;
+                    o4.x = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i]), l), __fdiv_rn(__uint_as_float(v[8 * i + 1]), l));
+                    o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
+                    o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
+                    o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
+                    // row r, 16-byte chunk c*4+i, stored at chunk slot (chunk ^ (r & 7)): conflict-free
+                    *reinterpret_cast<uint4*>(stage + r * kRowBytes + (((c * 4 + i) ^ (r & 7)) << 4)) = o4;
+                }
+            }
+            bar_sync(1 + j, 128);
+            const int64_t tile_off = z * a.osb + h * a.osh + (int64_t)qb * kTile * a.osn;
+            const int ch = r & 15;
+#pragma unroll 4
+            for (int it = 0; it < 16; ++it) {
+                const int row = it * 8 + (r >> 4);
+                const uint4 val = *reinterpret_cast<const uint4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
+                const int64_t off = tile_off + (int64_t)row * a.osn + ch * 8;
+                if (ta.n_peers == 0) {
+                    *reinterpret_cast<uint4*>(a.out + off) = val;
+                } else {
+                    // head-parallel runs: the rows go straight into every rank's copy of the
+                    // assembled output (16-byte stores, a row per 16 threads, over NVLink);
+                    // no collective follows
+                    for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint4*>(ta.peers[pr] + off) = val;
+                }
+            }
+        }
+    }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -227,234 +489,20 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     if (warp < 8) {
         // =================================================== softmax warps
         setmaxnreg_inc<AA_SOFTMAX_REGS>();
-        const int j = warp >> 2;
-        const int r = tid & 127;
-        const int qb = 2 * pair + j;
-        const int row_g = qb * kTile + r;
-        const int64_t srow = (int64_t)hz * a.N + row_g;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tS = tmem_base + lane_base + (uint32_t)j * 128u;
-        const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)j * 128u;
-
-        // Q tile: load, scale, round, store in the K-major 128B-swizzled layout the MMA reads
-        {
-            const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
-            const float c1 = bf16_round(a.sm_scale), c2 = bf16_round(kLog2e);
-            uint8_t* qs = smem + j * kTileBytes;
-#pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-                const int id = r + 128 * i;
-                const int rr = id >> 4, ch = id & 15;
-                uint4 raw = *reinterpret_cast<const uint4*>(qbase + (int64_t)rr * a.q.sn + ch * 8);
-                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float2 f = __bfloat1622float2(p2[e]);
-                    if (MODE == kWindow) {
-                        f.x = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.x, c1)), c2));
-                        f.y = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.y, c1)), c2));
-                    } else {
-                        f.x = __fmul_rn(__fmul_rn(f.x, a.sm_scale), kLog2e);
-                        f.y = __fmul_rn(__fmul_rn(f.y, a.sm_scale), kLog2e);
-                    }
-                    p2[e] = __floats2bfloat162_rn(f.x, f.y);
-                }
-                *reinterpret_cast<uint4*>(qs + sw_off(rr, ch)) = raw;
-            }
-            fence_proxy_async();
-            mbar_arrive(q_full(j));
+        SoftmaxCtx sc;
+        sc.smem = smem;
+        sc.tmem_base = tmem_base;
+        sc.abort_flag = abort_flag;
+        for (int jj = 0; jj < 2; ++jj) {
+            sc.q_full[jj] = q_full(jj);
+            sc.s_full[jj] = s_full(jj);
+            sc.p_ready[jj] = p_ready(jj);
+            sc.p_ready2[jj] = p_ready2(jj);
+            sc.o_done[jj] = o_done(jj);
         }
-
-        float m_true, m_ref, l;
-        if (MODE == kStripe) {
-            m_true = m_ref = a.M[srow];
-            l = a.L[srow];
-            if (ntiles > 0) {
-                const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 x = src[c * 8 + i];
-                        v[4 * i] = __float_as_uint(x.x);
-                        v[4 * i + 1] = __float_as_uint(x.y);
-                        v[4 * i + 2] = __float_as_uint(x.z);
-                        v[4 * i + 3] = __float_as_uint(x.w);
-                    }
-                    tmem_st32(tO + c * 32, v);
-                }
-                tmem_wait_st();
-            }
-        } else {
-            m_true = m_ref = -INFINITY;
-            l = 0.f;
-        }
-
-        bool ok = true;
-        for (int t = 0; t < ntiles && ok; ++t) {
-            ok = mbar_wait(s_full(j), t & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tcgen05_fence_after();
-            uint32_t sv[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
-            tmem_wait_ld();
-
-            if (MODE == kWindow) {
-                const int col0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
-                if (col0 + kTile - 1 > qb * kTile) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (col0 + c * 32 + i > row_g)
-                                sv[c][i] = __float_as_uint(__uint_as_float(sv[c][i]) + -1e6f);
-                }
-            } else {
-                const int valid = count - t * kTile;
-                if (valid < kTile) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i >= valid) sv[c][i] = __float_as_uint(-INFINITY);
-                }
-            }
-            {   // row maximum: four independent chains of three-input max
-                float mx[4] = {m_true, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
-                m_true = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            }
-            // move the exponent reference only when some row of the warp needs it
-            if (__any_sync(0xffffffffu, m_true > m_ref + kRescaleThreshold)) {
-                const float alpha = fast_exp2(m_ref - m_true);
-                if (!(MODE == kWindow && t == 0)) {
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(tO + c * 32, v);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tO + c * 32, v);
-                    }
-                }
-                l *= alpha;
-                m_ref = m_true;
-            }
-            float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-            const float2 neg_ref = make_float2(-m_ref, -m_ref);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pk[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int e = c * 64 + 2 * i;
-                    const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
-                                                            __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
-                    // kPolyShare of every 4 element pairs take the polynomial on the FMA pipe,
-                    // the others the MUFU unit: both pipes are busy
-                    const float2 p = ((i & 3) < kPolyShare) ? exp2_poly2(d) : make_float2(fast_exp2(d.x), fast_exp2(d.y));
-                    rs[i & 3] = __fadd2_rn(rs[i & 3], p);
-                    pk[i] = pack_bf16x2(p.x, p.y);
-                }
-                tmem_st32(tS + c * 32, pk);
-                // the first 64 columns of P are enough for the first four k-steps of P V
-                if (kSplitP || c == 1) {
-                    tmem_wait_st();
-                    tcgen05_fence_before();
-                    mbar_arrive((kSplitP && c == 1) ? p_ready2(j) : p_ready(j));
-                }
-            }
-            const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
-            l += rsum.x + rsum.y;
-        }
-
-        // ---- epilogue ----
-        if (ok && ntiles > 0) {
-            ok = mbar_wait(o_done(j), 0, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            tcgen05_fence_after();
-        }
-        if (MODE == kWindow) {
-            if (ok) {
-                const float sc = fast_exp2(m_ref - m_true);
-                a.M[srow] = m_true;
-                a.L[srow] = l * sc;
-                float4* dst = reinterpret_cast<float4*>(a.Acc + srow * kD);
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tO + c * 32, v);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        dst[c * 8 + i] = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
-                                                     __uint_as_float(v[4 * i + 2]) * sc,
-                                                     __uint_as_float(v[4 * i + 3]) * sc);
-                }
-            }
-        } else {
-            // The 128 rows of the tile are staged in shared memory (the tile's query buffer, which
-            // no MMA reads any more) and then written out as whole 256-byte rows by consecutive
-            // threads: coalesced stores, which matters most when the destination is another GPU.
-            // All 128 threads of the tile get here; they first agree that none of them gave up.
-            const bool all_ok = bar_and(1 + j, 128, ok);
-            if (all_ok) {
-                uint8_t* stage = smem + j * kTileBytes;
-                const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    if (ntiles > 0) {
-                        tmem_ld32(tO + c * 32, v);
-                        tmem_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float4 x = src[c * 8 + i];
-                            v[4 * i] = __float_as_uint(x.x);
-                            v[4 * i + 1] = __float_as_uint(x.y);
-                            v[4 * i + 2] = __float_as_uint(x.z);
-                            v[4 * i + 3] = __float_as_uint(x.w);
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 o4;
-                        o4.x = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i]), l), __fdiv_rn(__uint_as_float(v[8 * i + 1]), l));
-                        o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
-                        o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
-                        o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
-                        // row r, 16-byte chunk c*4+i, stored at chunk slot (chunk ^ (r & 7)): conflict-free
-                        *reinterpret_cast<uint4*>(stage + r * kRowBytes + (((c * 4 + i) ^ (r & 7)) << 4)) = o4;
-                    }
-                }
-                bar_sync(1 + j, 128);
-                const int64_t tile_off = z * a.osb + h * a.osh + (int64_t)qb * kTile * a.osn;
-                const int ch = r & 15;
-#pragma unroll 4
-                for (int it = 0; it < 16; ++it) {
-                    const int row = it * 8 + (r >> 4);
-                    const uint4 val = *reinterpret_cast<const uint4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
-                    const int64_t off = tile_off + (int64_t)row * a.osn + ch * 8;
-                    if (ta.n_peers == 0) {
-                        *reinterpret_cast<uint4*>(a.out + off) = val;
-                    } else {
-                        // head-parallel runs: the rows go straight into every rank's copy of the
-                        // assembled output (16-byte stores, a row per 16 threads, over NVLink);
-                        // no collective follows
-                        for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint4*>(ta.peers[pr] + off) = val;
-                    }
-                }
-            }
-        }
+        sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
+        sc.ntiles = ntiles; sc.n_init = n_init; sc.local_start = local_start; sc.count = count;
+        softmax_role<MODE, false>(ta, sc, tid);
     } else {
         setmaxnreg_dec<AA_OTHER_REGS>();
         if (warp == 8 && ntiles > 0) {
