@@ -136,8 +136,7 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, u
 }
 
 // What the softmax warps need to know about their CTA: where the tiles and barriers are.
-// q_full / p_ready / p_ready2 are arrived on (shared::cluster addresses when CLUSTER, so that
-// they may belong to the leader CTA of a pair), s_full / o_done are waited on (always local).
+// q_full / p_ready / p_ready2 are arrived on, s_full / o_done are waited on.
 struct SoftmaxCtx {
     uint8_t* smem;
     uint32_t tmem_base;
@@ -146,16 +145,8 @@ struct SoftmaxCtx {
     int pair, z, h, hz, ntiles, n_init, local_start, count;
 };
 
-template <bool CLUSTER>
-__device__ __forceinline__ void arrive_on(uint32_t bar) {
-    if (CLUSTER)
-        mbar_arrive_cluster(bar);
-    else
-        mbar_arrive(bar);
-}
-
 // The softmax role of warps 0-7 (see the file header): thread r of tile j owns query row r.
-template <int MODE, bool CLUSTER>
+template <int MODE>
 __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx& cx, int tid) {
     const AttendArgs& a = ta.a;
     const int warp = tid >> 5;
@@ -202,7 +193,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
             *reinterpret_cast<uint4*>(qs + sw_off(rr, ch)) = raw;
         }
         fence_proxy_async();
-        arrive_on<CLUSTER>(q_full_j);
+        mbar_arrive(q_full_j);
     }
 
     float m_true, m_ref, l;
@@ -309,7 +300,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
             if (kSplitP || c == 1) {
                 tmem_wait_st();
                 tcgen05_fence_before();
-                arrive_on<CLUSTER>((kSplitP && c == 1) ? p_ready2_j : p_ready_j);
+                mbar_arrive((kSplitP && c == 1) ? p_ready2_j : p_ready_j);
             }
         }
         const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
@@ -502,7 +493,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         }
         sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
         sc.ntiles = ntiles; sc.n_init = n_init; sc.local_start = local_start; sc.count = count;
-        softmax_role<MODE, false>(ta, sc, tid);
+        softmax_role<MODE>(ta, sc, tid);
     } else {
         setmaxnreg_dec<AA_OTHER_REGS>();
         if (warp == 8 && ntiles > 0) {
