@@ -61,3 +61,36 @@ def test_gather_heads_two_ranks():
         ret = m.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def _worker_missing_peer(rank, world, port, ret):
+    """Rank 1 leaves between steps (before the exchange); rank 0 must get an error from its
+    collective within the short process-group timeout instead of waiting for ever."""
+    from datetime import timedelta
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=5))
+    local = torch.zeros(1, 16, 2, 16, dtype=torch.bfloat16)
+    gather_heads(local)                         # step 1: everybody takes part
+    if rank == 1:
+        ret[rank] = "left"
+        return                                  # leaves with nothing in flight
+    try:
+        gather_heads(local)                     # step 2: the peer never joins
+        ret[rank] = "no error"
+    except Exception as e:                      # noqa: BLE001 - any failure report is what we want
+        ret[rank] = "error: " + type(e).__name__
+
+
+def test_missing_rank_is_reported_not_waited_for():
+    world, port = 2, _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        ctx = mp.spawn(_worker_missing_peer, args=(world, port, ret), nprocs=world, join=False)
+        for p in ctx.processes:
+            p.join(timeout=60)
+        alive = [p for p in ctx.processes if p.is_alive()]
+        for p in alive:
+            p.terminate()
+        assert not alive, "a rank was still waiting for its missing peer after 60 s"
+        assert ret.get(1) == "left"
+        assert str(ret.get(0, "")).startswith("error"), dict(ret)
