@@ -17,6 +17,7 @@ EXPORTS = [
     "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
     "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
+    "aa_selftest_wait_timeout",
 ]
 MAX_PEERS = 8
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -78,7 +79,8 @@ def load():
     lib.aa_workspace_layout.argtypes = [P, ctypes.POINTER(AALayout)]
     lib.aa_id_row_offset.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.aa_id_row_offset.restype = ctypes.c_int64
-    for name in ("aa_forward", "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status"):
+    for name in ("aa_forward", "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
+                 "aa_selftest_wait_timeout"):
         getattr(lib, name).argtypes = [P, ctypes.c_void_p]
         getattr(lib, name).restype = ctypes.c_int
     lib.aa_step2_stripes_static.argtypes = [ctypes.POINTER(AAStripesStaticArgs), ctypes.c_void_p]

@@ -432,6 +432,19 @@ int aa_check_status(const aa_params_t* p, void* stream) {
     return status[0] == 0 ? AA_OK : AA_ERR_DEVICE_TIMEOUT;
 }
 
+int aa_selftest_wait_timeout(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    rc = clear_status(p, lay, st);
+    if (rc) return rc;
+    aa::tc::wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(ws_ptr<int32_t>(p, lay.status_off));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch wait self-test");
+    return AA_OK;
+}
+
 int aa_total_selected(const aa_params_t* p, void* stream, int64_t* total) {
     if (!total) return AA_ERR_NULL;
     aa_workspace_layout_t lay;

@@ -692,5 +692,24 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// Self-test of the bounded-wait path: one warp waits on a barrier that nothing ever arrives
+// on; the wait gives up after its poll limit, raises the abort flag and the status word is
+// set exactly as the attention kernels set it.  Nothing faults, the context stays usable.
+__global__ void __launch_bounds__(32, 1) wait_timeout_selftest_kernel(int32_t* status) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+    const uint32_t bar_u = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(bar_u, 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(bar_u, 0, abort_flag);
+    __syncwarp();
+    if (threadIdx.x == 0 && (!ok || *abort_flag)) atomicMax(status, 1);
+}
+
 }  // namespace tc
 }  // namespace aa

@@ -135,6 +135,12 @@ int aa_step3_sparse_push(const aa_params_t *p, const aa_push_t *push, void *stre
  * or AA_ERR_DEVICE_TIMEOUT / AA_ERR_CUDA. */
 int aa_check_status(const aa_params_t *p, void *stream);
 
+/* Self-test of the failure path: enqueues a one-warp kernel that waits on a barrier nothing
+ * arrives on.  Its bounded wait gives up (about half a second), sets the workspace's status
+ * word and returns; a following aa_check_status reports AA_ERR_DEVICE_TIMEOUT.  No fault, no
+ * trap: the CUDA context stays usable.  (No counterpart in the reference.) */
+int aa_selftest_wait_timeout(const aa_params_t *p, void *stream);
+
 /* Sum of all counts as computed by the last aa_step2_stripes on this
  * workspace, written to *total (synchronises the stream).  The numerator of the
  * reference's sparsity ratio (anchor_attn_v4.py:271). */

@@ -262,3 +262,23 @@ def test_batch_fused_qkv_and_padded_heads(lib):
     Kp, Vp = padded(K), padded(V)
     assert Kp.stride(1) == N * 128 + 8
     assert torch.equal(anchor_attn(Q, Kp, Vp, difference=theta, return_computational_ratio=False), base)
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(lib):
+    """A device-side wait that can never be satisfied gives up after its poll limit and sets
+    the status word; the host reads AA_ERR_DEVICE_TIMEOUT, and the next operator call on the
+    same context works (nothing trapped or faulted)."""
+    import ctypes
+    from anchor_attention_b200 import AnchorAttnCall, _lib
+    Q, K, V = (t.cuda() for t in make_inputs(4096, 2, 1, seed=71, rope=True))
+    call = AnchorAttnCall(Q, K, V, None, 128, 16, 12.0)
+    want = call.run().clone()
+    call.check_status()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.aa_selftest_wait_timeout(ctypes.byref(call.params), stream) == 0
+    assert lib.aa_check_status(ctypes.byref(call.params), stream) == -11            # AA_ERR_DEVICE_TIMEOUT
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        call.check_status()
+    got = call.run()                        # clears the status word again
+    call.check_status()
+    assert torch.equal(got, want)
