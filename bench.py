@@ -32,10 +32,10 @@ sys.path.insert(0, ROOT)
 H, HKV, D, BLOCK, STEP, THETA = 32, 8, 128, 128, 16, 12.0
 METRIC = "ms_per_layer_anchor_attn_prefill_128k_llama31_8b_heads"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step-3 launch per K/V tile pair a
-# CTA loads, from an ncu capture at 32768 tokens (2.68 GB for 483,840 tile-pair loads of 64 KB each;
+# CTA loads, from an ncu capture at 32768 tokens (1.25 GB for 483,840 tile-pair loads of 64 KB each;
 # profiles/attend_tc_seq32768.md).  The full-size launch is not captured; its traffic is this figure
 # times its tile-pair loads, which assumes the same L2 hit rate.
-STEP3_DRAM_BYTES_PER_TILE_PAIR = 2.68e9 / 483840
+STEP3_DRAM_BYTES_PER_TILE_PAIR = 1.248e9 / 483840
 
 
 def algorithmic_flops(N, H, counts_total, step=STEP):
