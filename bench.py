@@ -31,11 +31,11 @@ sys.path.insert(0, ROOT)
 
 H, HKV, D, BLOCK, STEP, THETA = 32, 8, 128, 128, 16, 12.0
 METRIC = "ms_per_layer_anchor_attn_prefill_128k_llama31_8b_heads"
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step-3 launch per K/V tile pair a
-# CTA loads, from an ncu capture at 32768 tokens (1.25 GB for 483,840 tile-pair loads of 64 KB each;
-# profiles/attend_tc_seq32768.md).  The full-size launch is not captured; its traffic is this figure
-# times its tile-pair loads, which assumes the same L2 hit rate.
-STEP3_DRAM_BYTES_PER_TILE_PAIR = 1.248e9 / 483840
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step-3 launch at density 1 on one
+# GPU, from single-pass ncu captures of this benchmark (profiles/attend_tc_seq32768.md): sequence
+# length -> (bytes, K/V tile-pair loads of 64 KB by all CTAs).  Other sizes, densities and per-rank
+# shares are scaled from the nearest entry by their tile-pair loads.
+STEP3_DRAM_CAPTURES = {32768: (1.245e9, 483840), 131072: (7.97e9, 8225280)}
 
 
 def algorithmic_flops(N, H, counts_total, step=STEP):
@@ -312,7 +312,9 @@ def run_ours(args):
         f3_rank = f3 / W                               # the launch timed on one rank handles 1/W of the heads
         achieved = f3_rank / (k3_ms * 1e-3) / 1e12
         tile_pair_loads = counts_all / W * (G // (2 * BLOCK)) / BLOCK     # ids x 8 query-tile pairs / 128 ids per tile
-        traffic = STEP3_DRAM_BYTES_PER_TILE_PAIR * tile_pair_loads
+        ref_n = min(STEP3_DRAM_CAPTURES, key=lambda n: abs(n - N))
+        ref_bytes, ref_loads = STEP3_DRAM_CAPTURES[ref_n]
+        traffic = ref_bytes * tile_pair_loads / ref_loads
         line = {
             "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": W, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
@@ -329,7 +331,7 @@ def run_ours(args):
             "layer_tflops": (f1 + f2 + f3) / (ms * 1e-3) / 1e12,
             "roofline": {"kernel": "step 3 (gathered sparse flash attention)", "bound": "tensor",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                         "traffic": traffic, "traffic_unit": "bytes per launch (ncu at 32768 tokens, scaled by tile loads)",
+                         "traffic": traffic, "traffic_unit": f"DRAM bytes per launch (ncu capture at {ref_n} tokens, scaled by tile loads)",
                          "peak_source": f"{peak_src} (sustained bf16)", "launch_ms": k3_ms},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": W * sum(t.numel() * 2 for t in (hq, hk, hv)),
                     "d2h_bytes_per_step": W * hout.numel() * 2, "steps": e2e_steps},
