@@ -30,7 +30,7 @@ int check_shape(const aa_params_t* p) {
     if (p->B <= 0 || p->H <= 0 || p->Hkv <= 0 || p->N <= 0 || p->H % p->Hkv != 0) return AA_ERR_SHAPE;
     if (p->D != 128) return AA_ERR_HEAD_DIM;
     if (p->step != 16 && p->step != 32) return AA_ERR_STEP;
-    if (p->block_size != 128) return AA_ERR_BLOCK;
+    if (p->block_size != 64 && p->block_size != 128 && p->block_size != 256) return AA_ERR_BLOCK;
     if (p->N % (p->block_size * p->step) != 0) return AA_ERR_SEQ;
     if (p->dtype != AA_BF16) return AA_ERR_DTYPE;
     if ((int64_t)p->N * p->H * p->B > (int64_t)1 << 40) return AA_ERR_TOO_LARGE;
@@ -86,6 +86,7 @@ aa::AttendArgs attend_args(const aa_params_t* p, const aa_workspace_layout_t& la
     a.Hkv = p->Hkv;
     a.N = p->N;
     a.step = p->step;
+    a.block = p->block_size;
     a.sm_scale = (float)scale_of(p);
     return a;
 }
@@ -240,15 +241,15 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     return AA_OK;
 }
 
-// Pooled queries [B*H, N/128, 128] bf16 (contiguous) as a 3-D tensor map; box = 64 elements x
+// Pooled queries [B*H, N/block, 128] bf16 (contiguous) as a 3-D tensor map; box = 64 elements x
 // `step` rows (the pooled rows of one query head and big block), 128-byte swizzle.
-int make_qpool_map(CUtensorMap* map, const void* qpool, int BH, int N, int step) {
+int make_qpool_map(CUtensorMap* map, const void* qpool, int BH, int N, int step, int block) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) {
         snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
         return AA_ERR_CUDA;
     }
-    const cuuint64_t rows = (cuuint64_t)N / 128;
+    const cuuint64_t rows = (cuuint64_t)(N / block);
     cuuint64_t gdim[3] = {128, rows, (cuuint64_t)BH};
     cuuint64_t gstr[2] = {256, rows * 256};
     cuuint32_t box[3] = {64, (cuuint32_t)step, 1};
@@ -263,10 +264,24 @@ int make_qpool_map(CUtensorMap* map, const void* qpool, int BH, int N, int step)
     return AA_OK;
 }
 
+// Block-mean queries and anchors for pooling block size `block` (64, 128 or 256).
+int launch_pool(aa::TensorView q, const float* M, __nv_bfloat16* qpool, float* apool, int B, int H, int N, int block,
+                cudaStream_t st) {
+    const dim3 grid(N / block, H, B);
+    if (block == 64)
+        aa::pool_kernel<64><<<grid, 64, 0, st>>>(q, M, qpool, apool, H, N);
+    else if (block == 128)
+        aa::pool_kernel<128><<<grid, 64, 0, st>>>(q, M, qpool, apool, H, N);
+    else
+        aa::pool_kernel<256><<<grid, 64, 0, st>>>(q, M, qpool, apool, H, N);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AA_OK : cuda_fail(e, "launch pool");
+}
+
 // The scoring pass of step 2 (csrc/score_tc.cuh) for NB > 1.
 int launch_score(const void* k, int64_t ksb, int64_t ksh, int64_t ksn, const __nv_bfloat16* qpool, const float* apool,
-                 uint32_t* bitmap, int32_t* status, int B, int H, int Hkv, int N, int step, float qk_scale, float diff,
-                 cudaStream_t st) {
+                 uint32_t* bitmap, int32_t* status, int B, int H, int Hkv, int N, int step, int block, float qk_scale,
+                 float diff, cudaStream_t st) {
     if (!(qk_scale > 0.f)) return AA_ERR_SHAPE;      // the kernel relies on scores growing with the dot product
     static thread_local int configured_dev = -1;
     int dev = 0;
@@ -280,14 +295,15 @@ int launch_score(const void* k, int64_t ksb, int64_t ksh, int64_t ksn, const __n
     }
     aa::sc::ScoreArgs sa;
     sa.apool = apool; sa.bitmap = bitmap; sa.B = B; sa.H = H; sa.Hkv = Hkv; sa.N = N; sa.step = step;
+    sa.block = block;
     sa.qk_scale = qk_scale; sa.diff = diff; sa.status = status;
     CUtensorMap kmap, qmap;
     int rc = make_kv_map(&kmap, k, ksb, ksh, ksn, B, Hkv, N, &sa.kpos_n, &sa.kpos_h, &sa.kpos_b);
     if (rc) return rc;
-    rc = make_qpool_map(&qmap, qpool, B * H, N, step);
+    rc = make_qpool_map(&qmap, qpool, B * H, N, step, block);
     if (rc) return rc;
-    const int NB = N / (128 * step), Hg = H / Hkv;
-    const int max_tiles = (NB - 1) * step - 2;
+    const int G = block * step, NB = N / G, Hg = H / Hkv;
+    const int max_tiles = (((NB - 1) * G - block - 1) >> 7) - block / 128 + 1;      // candidate tiles of the last big block
     const int units_per_cta = 2 * (128 / step);
     dim3 grid((max_tiles + aa::sc::kTilesPerCta - 1) / aa::sc::kTilesPerCta,
               ((NB - 1) * Hg + units_per_cta - 1) / units_per_cta, B * Hkv);
@@ -370,19 +386,19 @@ int aa_step2_stripes(const aa_params_t* p, void* stream) {
     int32_t* counts = ws_ptr<int32_t>(p, lay.counts_off);
     int32_t* ids = ws_ptr<int32_t>(p, lay.ids_off);
 
-    aa::pool_kernel<<<dim3(p->N / 128, p->H, p->B), 64, 0, st>>>(
-        view(p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n), ws_ptr<float>(p, lay.m_off), qpool, apool, p->H,
-        p->N);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "launch pool");
+    int rcp = launch_pool(view(p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n), ws_ptr<float>(p, lay.m_off), qpool, apool,
+                          p->B, p->H, p->N, p->block_size, st);
+    if (rcp) return rcp;
+    cudaError_t e = cudaSuccess;
 
     if (NB > 1) {
         int rc2 = launch_score(p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, qpool, apool, bitmap,
-                               ws_ptr<int32_t>(p, lay.status_off), p->B, p->H, p->Hkv, p->N, p->step, qk_scale, diff, st);
+                               ws_ptr<int32_t>(p, lay.status_off), p->B, p->H, p->Hkv, p->N, p->step, p->block_size, qk_scale,
+                               diff, st);
         if (rc2) return rc2;
     }
     aa::compact_kernel<<<dim3(NB, p->H, p->B), 256, 0, st>>>(bitmap, ids, counts, p->H, p->N, p->step,
-                                                            lay.ids_per_head);
+                                                            p->block_size, lay.ids_per_head);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch compact");
     return AA_OK;
@@ -525,7 +541,7 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     if (((uintptr_t)a->q | (uintptr_t)a->k) & 15) return AA_ERR_STRIDE;
 
     // carve the three intermediates out of the fixed array; refuse what does not fit
-    const size_t BH = (size_t)a->B * a->H, nblk = (size_t)a->N / 128;
+    const size_t BH = (size_t)a->B * a->H, nblk = (size_t)a->N / a->block_size;
     const int NB = a->N / (a->block_size * a->step);
     const size_t qpool_off = 0;
     const size_t apool_off = align_up(qpool_off + BH * nblk * aa::kRowBytes);
@@ -548,21 +564,21 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     const float diff = (float)(a->theta * 1.44269504);
     const int64_t ids_per_head = aa_id_row_offset(a->block_size, a->step, NB);
 
-    aa::pool_kernel<<<dim3(a->N / 128, a->H, a->B), 64, 0, s>>>(
-        view(a->q, a->q_stride_b, a->q_stride_h, a->q_stride_n), a->anchors, qpool, apool, a->H, a->N);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "launch pool (static)");
+    int rcp = launch_pool(view(a->q, a->q_stride_b, a->q_stride_h, a->q_stride_n), a->anchors, qpool, apool, a->B, a->H,
+                          a->N, a->block_size, s);
+    if (rcp) return rcp;
+    cudaError_t e = cudaSuccess;
     if (NB > 1) {
         // the status word of the bounded device-side waits lives at the end of the fixed array
         int32_t* status = reinterpret_cast<int32_t*>(sc + AA_STATIC_SCRATCH_BYTES - 256);
         cudaError_t em = cudaMemsetAsync(status, 0, sizeof(int32_t), s);
         if (em != cudaSuccess) return cuda_fail(em, "cudaMemsetAsync(static status)");
         int rc2 = launch_score(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_n, qpool, apool, bitmap, status, a->B,
-                               a->H, a->Hkv, a->N, a->step, qk_scale, diff, s);
+                               a->H, a->Hkv, a->N, a->step, a->block_size, qk_scale, diff, s);
         if (rc2) return rc2;
     }
     aa::compact_kernel<<<dim3(NB, a->H, a->B), 256, 0, s>>>(bitmap, a->ids, a->counts, a->H, a->N, a->step,
-                                                           ids_per_head);
+                                                           a->block_size, ids_per_head);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch compact (static)");
     return AA_OK;
@@ -575,7 +591,7 @@ const char* aa_strerror(int code) {
         case AA_ERR_SHAPE: return "bad shape: B, H, Hkv, N must be positive and Hkv must divide H";
         case AA_ERR_HEAD_DIM: return "head dimension must be 128";
         case AA_ERR_STEP: return "Invalid step size. Only step sizes 16 or 32 are supported.";
-        case AA_ERR_BLOCK: return "block_size must be 128";
+        case AA_ERR_BLOCK: return "block_size must be 64, 128 or 256";
         case AA_ERR_SEQ: return "Sequence length must be divisible by (block_size * step)";
         case AA_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
         case AA_ERR_STRIDE: return "pointers must be 16-byte aligned and strides multiples of 8 elements";

@@ -433,7 +433,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     const int z = hz / a.H, h = hz % a.H;
     const int kvh = h / (a.H / a.Hkv);
 #endif
-    const int G = 128 * a.step;
+    const int G = a.block * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;
 
@@ -448,7 +448,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     } else {
         count = a.counts[(int64_t)hz * NB + b];
         ntiles = (count + kTile - 1) / kTile;
-        const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 256 * (int64_t)(b - 1));
+        const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)a.block * (b - 1));
         idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
     }
 

@@ -30,7 +30,7 @@ struct AttendArgs {
     const int32_t* counts;
     const int32_t* ids;
     int64_t ids_per_head;
-    int B, H, Hkv, N, step;
+    int B, H, Hkv, N, step, block;      // block = pooling block size (64, 128 or 256); big block G = block * step
     float sm_scale;
 };
 

@@ -2,7 +2,8 @@
 //
 // Replaces the key-column loop of get_q_mask_triton (reference:
 // anchor_attn/src/ops/get_mask_test.py:93-121): for every big block b >= 1 and every
-// 128-column key tile t = 1 .. b*step - 2, the `step` block-pooled query rows of each
+// 128-column key tile that holds candidate columns [block, b*G - block), G = block*step
+// (for block = 128: tiles 1 .. b*step - 2), the `step` block-pooled query rows of each
 // query head are multiplied with the 128 keys; a column is hit for (head, b) when
 //     fp32(bf16(dot * qk_scale)) + diff >= anchor(row)          for some pooled row.
 // Output: one bit per (query head, big block, column) in the hit bitmap.
@@ -43,7 +44,7 @@ constexpr int kScSmemTotal = kScSmemA + kScSmemRing + 256 + 1024;
 struct ScoreArgs {
     const float* apool;        // [B, H, N/128] block-mean anchors (already rounded to bf16 values)
     uint32_t* bitmap;          // [B, H, NB, N/32]
-    int B, H, Hkv, N, step;
+    int B, H, Hkv, N, step, block;      // block = pooling block size; candidates of big block b: [block, b*G - block)
     float qk_scale, diff;
     int kpos_n, kpos_h, kpos_b;
     int32_t* status;
@@ -79,21 +80,24 @@ score_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
     // ---- which work item (uniform for the CTA; empty items leave before any set-up) ----
     const int step = a.step;
     const int Hg = a.H / a.Hkv;
-    const int NB = a.N / (128 * step);
+    const int G = a.block * step;
+    const int NB = a.N / G;
+    const int t_first = a.block / 128;               // first 128-column tile that holds candidates
+    auto t_last = [&](int b) { return (b * G - a.block - 1) >> 7; };   // last one of big block b
     const int upt = 128 / step;                      // units per A tile
     const int units_kv = (NB - 1) * Hg;
     const int u0 = blockIdx.y * 2 * upt;
     if (u0 >= units_kv) return;
     const int u_end = min(u0 + 2 * upt, units_kv);   // exclusive
     const int nA = (u_end - u0 + upt - 1) / upt;
-    const int t_begin = 1 + blockIdx.x * kTilesPerCta;
+    const int t_begin = t_first + blockIdx.x * kTilesPerCta;
     // tiles each A tile needs from this chunk: candidates of its last big block
     int nt[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int ul = min(u0 + (i + 1) * upt, u_end) - 1;            // last unit of tile i
         const int bmax = 1 + ul / Hg;
-        nt[i] = (i < nA) ? max(0, min(kTilesPerCta, bmax * step - 2 - t_begin + 1)) : 0;
+        nt[i] = (i < nA) ? max(0, min(kTilesPerCta, t_last(bmax) - t_begin + 1)) : 0;
     }
     const int ntiles = max(nt[0], nt[1]);
     if (ntiles <= 0) return;
@@ -148,11 +152,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant_
         const int words_per_row = a.N / 32;
         float thr = __uint_as_float(0x7FC00000u);
         if (valid) {
-            const float anchor = a.apool[(int64_t)(z * a.H + h) * (a.N / 128) + b * step + r % step];
+            const float anchor = a.apool[(int64_t)(z * a.H + h) * (a.N / a.block) + b * step + r % step];
             thr = pass_threshold(a.qk_scale, a.diff, anchor);
         }
         uint32_t* brow = a.bitmap + ((int64_t)(z * a.H + h) * NB + b) * words_per_row;
-        const int last_tile = b * step - 2;          // last candidate tile of this row's big block
+        const int last_tile = t_last(b);             // last candidate tile of this row's big block
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         bool ok = true;
         for (int tt = 0; tt < nt[i] && ok; ++tt) {

@@ -14,22 +14,25 @@
 namespace aa {
 
 // ---------------------------------------------------------------------------
-// pool_kernel: grid (N/128, H, B), 64 threads; thread t owns columns 2t, 2t+1.
-// The 128 rows are summed in bf16 in this order (the one the reference's compiled
+// pool_kernel: grid (N/BS, H, B), 64 threads; thread t owns columns 2t, 2t+1.  BS = pooling
+// block size (64, 128 or 256 rows).
+// The rows are summed in bf16 in this order (for BS = 128 the one the reference's compiled
 // reduction uses): rows 32w..32w+31 form group w and are reduced by halving
-// (i + 16, i + 8, i + 4, i + 2, i + 1); the four group sums are combined as
-// (W0 + W2) + (W1 + W3).  Division by 128 is exact.
-// Warp 0 also reduces the 128 anchors of the block (fp32, same tree).
+// (i + 16, i + 8, i + 4, i + 2, i + 1); the BS/32 group sums are combined by halving as well
+// (for four groups: (W0 + W2) + (W1 + W3)).  Division by BS is exact.
+// Warp 0 also reduces the BS anchors of the block (fp32, same tree).
 // ---------------------------------------------------------------------------
+template <int BS>
 __global__ void __launch_bounds__(64) pool_kernel(TensorView q, const float* __restrict__ M,
                                                   __nv_bfloat16* __restrict__ qpool, float* __restrict__ apool,
                                                   int H, int N) {
+    constexpr int NG = BS / 32;
     const int blk = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
     const int t = threadIdx.x;
-    const __nv_bfloat16* src = q.ptr + z * q.sb + h * q.sh + (int64_t)blk * 128 * q.sn + 2 * t;
-    __nv_bfloat162 w[4];
+    const __nv_bfloat16* src = q.ptr + z * q.sb + h * q.sh + (int64_t)blk * BS * q.sn + 2 * t;
+    __nv_bfloat162 w[NG];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
+    for (int g = 0; g < NG; ++g) {
         __nv_bfloat162 x[32];
 #pragma unroll
         for (int r = 0; r < 32; ++r)
@@ -40,23 +43,29 @@ __global__ void __launch_bounds__(64) pool_kernel(TensorView q, const float* __r
             for (int i = 0; i < half; ++i) x[i] = __hadd2(x[i], x[i + half]);
         w[g] = x[0];
     }
-    __nv_bfloat162 s = __hadd2(__hadd2(w[0], w[2]), __hadd2(w[1], w[3]));
-    float2 f = __bfloat1622float2(s);
-    __nv_bfloat162 mean = __floats2bfloat162_rn(f.x / 128.0f, f.y / 128.0f);
-    const int64_t prow = ((int64_t)(z * H + h) * (N / 128) + blk);
+#pragma unroll
+    for (int half = NG / 2; half >= 1; half >>= 1)
+#pragma unroll
+        for (int i = 0; i < half; ++i) w[i] = __hadd2(w[i], w[i + half]);
+    float2 f = __bfloat1622float2(w[0]);
+    __nv_bfloat162 mean = __floats2bfloat162_rn(f.x / (float)BS, f.y / (float)BS);
+    const int64_t prow = ((int64_t)(z * H + h) * (N / BS) + blk);
     *reinterpret_cast<__nv_bfloat162*>(qpool + prow * kD + 2 * t) = mean;
 
     if (t < 32) {
-        const float* m = M + (int64_t)(z * H + h) * N + (int64_t)blk * 128;
-        float v[4];
+        const float* m = M + (int64_t)(z * H + h) * N + (int64_t)blk * BS;
+        float v[NG];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) v[g] = m[g * 32 + t];
+        for (int g = 0; g < NG; ++g) v[g] = m[g * 32 + t];
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1)
 #pragma unroll
-            for (int g = 0; g < 4; ++g) v[g] = __fadd_rn(v[g], __shfl_xor_sync(0xffffffffu, v[g], off));
-        float a = __fadd_rn(__fadd_rn(v[0], v[2]), __fadd_rn(v[1], v[3]));
-        if (t == 0) apool[prow] = bf16_round(a / 128.0f);
+            for (int g = 0; g < NG; ++g) v[g] = __fadd_rn(v[g], __shfl_xor_sync(0xffffffffu, v[g], off));
+#pragma unroll
+        for (int half = NG / 2; half >= 1; half >>= 1)
+#pragma unroll
+            for (int i = 0; i < half; ++i) v[i] = __fadd_rn(v[i], v[i + half]);
+        if (t == 0) apool[prow] = bf16_round(v[0] / (float)BS);
     }
 }
 
@@ -66,20 +75,20 @@ __global__ void __launch_bounds__(64) pool_kernel(TensorView q, const float* __r
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) compact_kernel(const uint32_t* __restrict__ bitmap, int32_t* __restrict__ ids,
                                                       int32_t* __restrict__ counts, int H, int N, int step,
-                                                      int64_t ids_per_head) {
+                                                      int block, int64_t ids_per_head) {
     const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
-    const int NB = N / (128 * step);
+    const int NB = N / (block * step);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t hz = (int64_t)z * H + h;
     if (b == 0) {
         if (tid == 0) counts[hz * NB] = 0;
         return;
     }
-    const int nwords = (b * step - 2) * 4;        // candidate columns / 32
-    const int w0 = 4;                             // first candidate word (column 128)
+    const int G = block * step;
+    const int nwords = (b * G - 2 * block) / 32;  // candidate columns [block, b*G - block) / 32
+    const int w0 = block / 32;                    // first candidate word
     const uint32_t* row = bitmap + (hz * NB + b) * (int64_t)(N / 32);
-    const int G = 128 * step;
-    const int64_t row_off = (int64_t)G * b * (b - 1) / 2 - 256 * (int64_t)(b - 1);
+    const int64_t row_off = (int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)block * (b - 1);
     int32_t* dst = ids + hz * ids_per_head + row_off;
     __shared__ int warp_sums[8];
     __shared__ int base_s;

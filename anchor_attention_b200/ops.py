@@ -58,7 +58,7 @@ class AnchorAttnCall:
             "Q, K, V must be bfloat16"
         assert step in [16, 32], \
             f"Invalid step size: {step}. Only step sizes 16 or 32 are supported."
-        assert block_size == 128, f"block_size {block_size} is not supported (128 only)"
+        assert block_size in (64, 128, 256), f"block_size {block_size} is not supported (64, 128 or 256)"
         assert Q.size(-2) % (block_size * step) == 0, \
             f"Sequence length {Q.size(-2)} must be divisible by (block_size * step = {block_size * step})."
         B, H, N, D = Q.shape

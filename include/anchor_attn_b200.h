@@ -29,7 +29,7 @@ enum {
     AA_ERR_SHAPE = -2,         /* B/H/Hkv/N non-positive, H % Hkv != 0               */
     AA_ERR_HEAD_DIM = -3,      /* D != 128                                           */
     AA_ERR_STEP = -4,          /* step not in {16, 32}  (anchor_attn_v4.py:305)      */
-    AA_ERR_BLOCK = -5,         /* block_size != 128 (the only size any harness uses) */
+    AA_ERR_BLOCK = -5,         /* block_size not in {64, 128, 256}                   */
     AA_ERR_SEQ = -6,           /* N % (block_size*step) != 0 (anchor_attn_v4.py:308) */
     AA_ERR_WORKSPACE = -7,     /* workspace missing, misaligned or too small         */
     AA_ERR_STRIDE = -8,        /* a stride is not a multiple of 8 elements (16 B)    */
@@ -53,7 +53,10 @@ enum { AA_BF16 = 0 };
  */
 typedef struct aa_params {
     int32_t B, H, Hkv, N, D;
-    int32_t block_size;        /* 128 (patch.py:36-40 "block_size_M")                    */
+    int32_t block_size;        /* pooling block of step 2: 64, 128 or 256; the default of every
+                                  harness is 128 (patch.py:36-40 "block_size_M").  The big block is
+                                  block_size*step rows; steps 1 and 3 always work on 128-row tiles,
+                                  as the reference's do (anchor_attn_v4.py:232)              */
     int32_t step;              /* 16 or 32 (patch.py:36-40 "step")                       */
     int32_t dtype;             /* AA_BF16                                                */
     double  theta;             /* "difference"/theta in natural-log units, default 12;

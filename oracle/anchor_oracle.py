@@ -125,18 +125,23 @@ def step1(q, k, v, sm_scale, block_size=128, step=16, mode="bf16", blocks=None):
 # step 2
 # --------------------------------------------------------------------------
 def _tree_sum_rows(x: torch.Tensor, rd) -> torch.Tensor:
-    """Sum 128 rows of ``x`` [..., 128, C] in the order the compiled reference
-    kernel uses on the GPU: row r sits in lane r%32 of warp r//32; each warp
-    reduces with xor-butterflies at 16, 8, 4, 2, 1; the four warp partials are
-    combined as (W0+W2)+(W1+W3).  Every add is rounded by ``rd``."""
-    assert x.shape[-2] == 128
-    w = x.reshape(*x.shape[:-2], 4, 32, x.shape[-1])
+    """Sum the rows of ``x`` [..., BS, C] (BS = 64, 128 or 256) in the order the compiled
+    reference kernel uses on the GPU for BS = 128: row r sits in lane r%32 of warp r//32;
+    each group of 32 rows is reduced with xor-butterflies at 16, 8, 4, 2, 1; the BS/32 group
+    sums are combined by halving as well (four groups: (W0+W2)+(W1+W3)).  Every add is rounded
+    by ``rd``.  For BS = 64 and 256 this is the order of the CUDA pooling kernel; the order of
+    the reference's compiled reduction at those sizes has not been derived."""
+    bs = x.shape[-2]
+    assert bs in (64, 128, 256)
+    w = x.reshape(*x.shape[:-2], bs // 32, 32, x.shape[-1])
     for half in (16, 8, 4, 2, 1):
         w = rd(w[..., :half, :] + w[..., half:2 * half, :])
-    w = w[..., 0, :]                      # [..., 4, C]
-    a = rd(w[..., 0, :] + w[..., 2, :])
-    b = rd(w[..., 1, :] + w[..., 3, :])
-    return rd(a + b)
+    w = w[..., 0, :]                      # [..., BS/32, C]
+    half = bs // 64
+    while half >= 1:
+        w = rd(w[..., :half, :] + w[..., half:2 * half, :])
+        half //= 2
+    return w[..., 0, :]
 
 
 def _seq_sum_rows(x: torch.Tensor, rd) -> torch.Tensor:
@@ -154,7 +159,7 @@ def pool_q(q: torch.Tensor, block_size: int, mode: str, order: str = "tree") -> 
     rd = _rounder(mode)
     N, D = q.shape
     x = q.to(torch.float32).reshape(N // block_size, block_size, D)
-    if order == "tree" and block_size == 128:
+    if order == "tree" and block_size in (64, 128, 256):
         s = _tree_sum_rows(x, rd)
     elif order == "seq":
         s = _seq_sum_rows(x, rd)
@@ -168,7 +173,7 @@ def pool_anchor(M: torch.Tensor, block_size: int, mode: str, order: str = "tree"
     rounded to the input dtype."""
     rd = _rounder(mode)
     x = M.reshape(-1, block_size, 1)
-    if order == "tree" and block_size == 128:
+    if order == "tree" and block_size in (64, 128, 256):
         s = _tree_sum_rows(x, lambda t: t)[..., 0]
     else:
         s = x.sum(dim=1)[..., 0]

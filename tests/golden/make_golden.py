@@ -26,10 +26,12 @@ import time
 import numpy as np
 
 CASES = [
-    # name, N, H, Hkv, theta, rope, q_shift, seed
-    ("n4096_h2_t12", 4096, 2, 1, 12.0, False, 0.0, 0),
-    ("n6144_h1_t11_shift", 6144, 1, 1, 11.0, False, 0.5, 1),
-    ("n6144_h2_t10_shift_rope", 6144, 2, 1, 10.0, True, 0.5, 2),
+    # name, N, H, Hkv, theta, rope, q_shift, seed, block_size
+    ("n4096_h2_t12", 4096, 2, 1, 12.0, False, 0.0, 0, 128),
+    ("n6144_h1_t11_shift", 6144, 1, 1, 11.0, False, 0.5, 1, 128),
+    ("n6144_h2_t10_shift_rope", 6144, 2, 1, 10.0, True, 0.5, 2, 128),
+    ("n3072_h2_t10_shift_bs64", 3072, 2, 1, 10.0, True, 0.5, 3, 64),
+    ("n8192_h1_t10_shift_bs256", 8192, 1, 1, 10.0, True, 0.5, 4, 256),
 ]
 
 
@@ -68,7 +70,7 @@ def main():
     dev = "cuda" if gpu else "cpu"
     tag = "ref_gpu_bf16" if gpu else "ref_interp_fp16"
     want = set(filter(None, args.cases.split(",")))
-    for name, N, H, Hkv, theta, rope, q_shift, seed in CASES:
+    for name, N, H, Hkv, theta, rope, q_shift, seed, block in CASES:
         if want and name not in want:
             continue
         t0 = time.time()
@@ -80,16 +82,16 @@ def main():
         Vd = V.repeat_interleave(g, dim=1).to(dev).contiguous()
         B, _, _, D = Q.shape
         sm_scale = 1.0 / (D ** 0.5)
-        L, M, Acc = anchor_attn_step_1(Qd, Kd, Vd, 1, 1, 128, 16, B, H, N, D, sm_scale, 128, 128)
-        coords, counts = anchor_attn_step_2(Qd, Kd, M, 128, 16, theta * LOG2E, B, H, N, D, sm_scale)
-        out, ratio = anchor_attn(Qd, Kd, Vd, None, 128, 16, theta, True)
+        L, M, Acc = anchor_attn_step_1(Qd, Kd, Vd, 1, 1, block, 16, B, H, N, D, sm_scale, 128, 128)
+        coords, counts = anchor_attn_step_2(Qd, Kd, M, block, 16, theta * LOG2E, B, H, N, D, sm_scale)
+        out, ratio = anchor_attn(Qd, Kd, Vd, None, block, 16, theta, True)
         counts = counts.cpu().numpy()[0, :, :, 0]                 # [H, NB]
         coords = coords.cpu().numpy()[0]                          # [H, NB, N]
-        flat = np.concatenate([coords[h, b, :counts[h, b]] for h in range(H) for b in range(N // 2048)]
+        flat = np.concatenate([coords[h, b, :counts[h, b]] for h in range(H) for b in range(N // (block * 16))]
                               or [np.zeros(0, np.int32)]).astype(np.int32)
         np.savez_compressed(
             os.path.join(args.out, f"{tag}_{name}.npz"),
-            N=N, H=H, Hkv=Hkv, theta=theta, rope=rope, q_shift=q_shift, seed=seed,
+            N=N, H=H, Hkv=Hkv, theta=theta, rope=rope, q_shift=q_shift, seed=seed, block=block,
             inputs_sha256=csum, counts=counts, ids=flat,
             M=M.float().cpu().numpy()[0], L=L.float().cpu().numpy()[0],
             Acc_rows16=Acc.float().cpu().numpy()[0, :, ::16],

@@ -63,7 +63,7 @@ def test_workspace_layout(lib):
 
 
 @pytest.mark.parametrize("change,code", [
-    (dict(D=64), -3), (dict(step=8), -4), (dict(block=64), -5), (dict(N=3000), -6),
+    (dict(D=64), -3), (dict(step=8), -4), (dict(block=32), -5), (dict(N=3000), -6),
     (dict(H=3, Hkv=2), -2), (dict(N=0), -2),
 ])
 def test_shape_validation(lib, change, code):

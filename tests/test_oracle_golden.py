@@ -16,6 +16,11 @@ GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref
 GOLDEN_GPU = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_gpu_bf16_*.npz")))
 
 
+def _block(g):
+    """Pooling block size of a fixture (the first fixtures were written before the key existed)."""
+    return int(g["block"]) if "block" in g.files else 128
+
+
 def _inputs(g):
     return make_inputs(int(g["N"]), int(g["H"]), int(g["Hkv"]), seed=int(g["seed"]), rope=bool(g["rope"]),
                        dtype=torch.float16, q_shift=float(g["q_shift"]))
@@ -30,14 +35,16 @@ def test_oracle_matches_reference_kernels(path):
     g = np.load(path)
     Q, K, V = _inputs(g)
     # the interpreter sums the pooled queries left to right and adds diff in fp16
-    r = anchor_attn_oracle(Q, K, V, difference=float(g["theta"]), mode="fp16", order="seq", diff_add="input")
+    r = anchor_attn_oracle(Q, K, V, block_size=_block(g), difference=float(g["theta"]), mode="fp16", order="seq",
+                           diff_add="input")
     H = int(g["H"])
     assert r.counts[0].tolist() == g["counts"].tolist()
     flat = np.concatenate([x.numpy() for h in range(H) for x in r.ids[0][h]])
     assert flat.shape == g["ids"].shape and (flat == g["ids"]).all()          # bit-exact index sets
     assert np.array_equal(r.M[0].numpy(), g["M"])                               # row maxima exact
     assert np.max(np.abs(r.L[0].numpy() - g["L"]) / g["L"]) < 2e-6
-    assert np.max(np.abs(r.Acc[0, :, ::16].numpy() - g["Acc_rows16"])) < 2e-5
+    # fp32 accumulation-order noise grows with the window length (4096 keys at block 256)
+    assert np.max(np.abs(r.Acc[0, :, ::16].numpy() - g["Acc_rows16"])) < 2e-5 * max(1, _block(g) // 128)
     out_ref = g["out"].astype(np.float32)
     err = np.abs(r.out[0].numpy() - out_ref)
     assert err.max() <= 2e-2 and err.mean() <= 1e-3
@@ -55,13 +62,14 @@ def test_oracle_matches_reference_kernels_on_gpu_bf16(path):
     N, H, Hkv, theta = int(g["N"]), int(g["H"]), int(g["Hkv"]), float(g["theta"])
     Q, K, V = make_inputs(N, H, Hkv, seed=int(g["seed"]), rope=bool(g["rope"]), dtype=torch.bfloat16,
                           q_shift=float(g["q_shift"]))
-    r = anchor_attn_oracle(Q, K, V, difference=theta, mode="bf16", order="tree")
+    block = _block(g)
+    r = anchor_attn_oracle(Q, K, V, block_size=block, difference=theta, mode="bf16", order="tree")
     assert np.abs(r.M[0].numpy() - g["M"]).max() < 1e-4
     assert (np.abs(r.L[0].numpy() - g["L"]) / g["L"]).max() < 1e-4
     assert np.abs(r.Acc[0, :, ::16].numpy() - g["Acc_rows16"]).max() < 5e-3
     pos, diff, total = 0, 0, 0
     for h in range(H):
-        for b in range(N // 2048):
+        for b in range(N // (block * 16)):
             c = int(g["counts"][h, b])
             ref_ids = torch.from_numpy(g["ids"][pos:pos + c].astype(np.int32))
             pos += c
@@ -70,7 +78,7 @@ def test_oracle_matches_reference_kernels_on_gpu_bf16(path):
                 assert c == 0
                 continue
             # the reference's own list must sit inside our tie band classification ...
-            check_id_set(ref_ids, Q[0, h], K[0, h // (H // Hkv)], r.M[0, h], 128 ** -0.5, theta, b)
+            check_id_set(ref_ids, Q[0, h], K[0, h // (H // Hkv)], r.M[0, h], 128 ** -0.5, theta, b, block)
             diff += len(set(ref_ids.tolist()) ^ set(r.ids[0][h][b].tolist()))
     assert diff <= max(2, 0.01 * total), f"{diff} of {total} selected columns differ"
     out_ref = torch.from_numpy(g["out"]).view(torch.bfloat16).float()

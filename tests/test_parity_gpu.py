@@ -89,8 +89,10 @@ def test_against_reference_gpu_fixtures(lib, path):
     import numpy as np
     g = np.load(path)
     N, H, Hkv, theta = int(g["N"]), int(g["H"]), int(g["Hkv"]), float(g["theta"])
+    block = int(g["block"]) if "block" in g.files else 128
     Q, K, V = make_inputs(N, H, Hkv, seed=int(g["seed"]), rope=bool(g["rope"]), q_shift=float(g["q_shift"]))
-    call = _call(Q, K, V, theta)
+    from anchor_attention_b200 import AnchorAttnCall
+    call = AnchorAttnCall(Q.cuda(), K.cuda(), V.cuda(), None, block, 16, theta)
     out = call.run().float().cpu()
     call.check_status()
     assert (call.M.cpu()[0] - torch.from_numpy(g["M"])).abs().max() < 1e-4
@@ -102,13 +104,13 @@ def test_against_reference_gpu_fixtures(lib, path):
     pos = diff = total = 0
     Mref = torch.from_numpy(g["M"])
     for h in range(H):
-        for b in range(N // 2048):
+        for b in range(N // (block * 16)):
             c = int(g["counts"][h, b])
             ref_ids = g["ids"][pos:pos + c]
             pos += c
             total += c
             if b:
-                check_id_set(ours[0][h][b], Q[0, h], K[0, h // (H // Hkv)], Mref[h], SM, theta, b)
+                check_id_set(ours[0][h][b], Q[0, h], K[0, h // (H // Hkv)], Mref[h], SM, theta, b, block)
             diff += len(set(ref_ids.tolist()) ^ set(ours[0][h][b].tolist()))
     print(f"\n{__import__('os').path.basename(path)}: {total} selected by the reference, symmetric difference {diff}")
     assert diff <= max(2, 0.01 * total)
@@ -282,3 +284,36 @@ def test_bounded_wait_reports_timeout_and_context_survives(lib):
     got = call.run()                        # clears the status word again
     call.check_status()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("block,N,H,Hkv,theta", [(64, 4096, 4, 2, 10.0), (256, 8192, 2, 1, 10.0), (64, 2048, 2, 1, 12.0)])
+def test_other_pooling_block_sizes(lib, block, N, H, Hkv, theta):
+    """block_size 64 and 256 (big blocks of 1024 / 4096 rows, candidates [block, b*G - block)):
+    state, index sets up to the tie band and output against the oracle."""
+    from anchor_attention_b200 import AnchorAttnCall
+    Q, K, V = make_inputs(N, H, Hkv, seed=80 + block, rope=True, q_shift=0.5)
+    ref = anchor_attn_oracle(Q, K, V, block_size=block, difference=theta, mode="bf16", order="tree")
+    call = AnchorAttnCall(Q.cuda(), K.cuda(), V.cuda(), None, block, 16, theta)
+    out = call.run().float().cpu()
+    call.check_status()
+    assert (call.M.cpu() - ref.M).abs().max() < 2e-3
+    assert ((call.L.cpu() - ref.L).abs() / ref.L).max() < 2e-3
+    G = block * 16
+    ours, counts = call.id_lists(), call.counts.cpu()
+    total_diff = 0
+    for h in range(H):
+        for b in range(N // G):
+            ids = ours[0][h][b]
+            assert ids.numel() == counts[0, h, b]
+            if b == 0:
+                assert ids.numel() == 0
+                continue
+            assert (ids[1:] > ids[:-1]).all()
+            if ids.numel():
+                assert ids.min() >= block and ids.max() < b * G - block
+            check_id_set(ids, Q[0, h], K[0, h // (H // Hkv)], ref.M[0, h], SM, theta, b, block)
+            total_diff += len(set(ids.tolist()) ^ set(ref.ids[0][h][b].tolist()))
+    print(f"\nblock {block}: selected {int(counts.sum())}, symmetric difference to oracle {total_diff}")
+    assert int(counts.sum()) > 0
+    err = (out - ref.out).abs()
+    assert err.max() <= OUT_MAX_ABS and err.mean() <= OUT_MEAN_ABS
