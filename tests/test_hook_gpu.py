@@ -90,3 +90,29 @@ def test_host_buffer_entry_point_matches_device_call(lib):
     want = anchor_attn(Q.cuda(), K.cuda(), V.cuda(), difference=10.0, return_computational_ratio=False).cpu()
     got = anchor_attn_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), None, None, 128, 16, 10.0)
     assert got.shape == want.shape and torch.equal(got, want)
+
+
+def test_operator_replays_from_a_cuda_graph(lib):
+    """The five launches of one operator call can be captured into a CUDA graph (nothing in
+    the call allocates or synchronises) and replayed on new input values in the same buffers."""
+    from anchor_attention_b200 import AnchorAttnCall
+    Q, K, V = (t.cuda() for t in make_inputs(4096, 4, 2, seed=91, rope=True, q_shift=0.5))
+    Q2, K2, V2 = (t.cuda() for t in make_inputs(4096, 4, 2, seed=92, rope=True, q_shift=0.5))
+    want1 = AnchorAttnCall(Q, K, V, None, 128, 16, 10.0).run().clone()
+    want2 = AnchorAttnCall(Q2, K2, V2, None, 128, 16, 10.0).run().clone()
+    q, k, v = Q.clone(), K.clone(), V.clone()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        call = AnchorAttnCall(q, k, v, None, 128, 16, 10.0)
+        call.run()                                   # warm-up outside the capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            call.run()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(call.out, want1)
+    q.copy_(Q2); k.copy_(K2); v.copy_(V2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(call.out, want2)
