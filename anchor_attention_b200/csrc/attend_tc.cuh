@@ -172,11 +172,18 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
         const float c1 = bf16_round(a.sm_scale), c2 = bf16_round(kLog2e);
         uint8_t* qs = smem + j * kTileBytes;
-#pragma unroll 4
+        // all sixteen loads of the thread are issued before the first one is used
+        uint4 raws[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int id = r + 128 * i;
+            raws[i] = *reinterpret_cast<const uint4*>(qbase + (int64_t)(id >> 4) * a.q.sn + (id & 15) * 8);
+        }
+#pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int id = r + 128 * i;
             const int rr = id >> 4, ch = id & 15;
-            uint4 raw = *reinterpret_cast<const uint4*>(qbase + (int64_t)rr * a.q.sn + ch * 8);
+            uint4 raw = raws[i];
             __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {

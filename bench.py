@@ -115,10 +115,10 @@ def measured_peaks():
 # --------------------------------------------------------------------------
 # CPU legs (the only places the oracle is executed by the benchmark)
 # --------------------------------------------------------------------------
-def cpu_sample(N, threads=None, budget_s=12.0):
+def cpu_sample(N, threads=None, limit_s=12.0):
     """Time the CPU restatement on a bounded sample of the workload: one query head
     of the N-token layer, whole big blocks (2048 query rows each, all three steps)
-    taken from the last one downwards until ``budget_s`` seconds are spent, then
+    taken from the last one downwards until ``limit_s`` seconds are spent, then
     scaled by the layer's query-key pair count.  Returns (extrapolated ms per
     layer, description, cores)."""
     import torch
@@ -137,7 +137,7 @@ def cpu_sample(N, threads=None, budget_s=12.0):
         window = G * (G + 1) // 2 + (G * G if b > 0 else 0)
         sample_pairs += window + G * int(ids[b].numel())
         blocks.append(b)
-        if dt >= budget_s:
+        if dt >= limit_s:
             break
     cap_total = sum(bb * G - 2 * BLOCK for bb in range(1, NB))
     layer_pairs = H * (G * (G + 1) // 2 + (NB - 1) * (G * G + G * (G + 1) // 2) + G * cap_total)
