@@ -197,7 +197,9 @@ def run_ours(args):
     N = args.seq
     q_lo, q_hi, kv_lo, kv_hi = head_partition(H, HKV, W, rank)
     h = q_hi - q_lo
-    Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, heads=(q_lo, q_hi, kv_lo, kv_hi))
+    THETA = args.theta          # 12 unless the auxiliary sparse-regime run is asked for
+    Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, heads=(q_lo, q_hi, kv_lo, kv_hi),
+                          q_shift=args.q_shift)
     push = W > 1 and args.exchange == "push"
     exchange_note = ""
     if push:
@@ -315,10 +317,12 @@ def run_ours(args):
         ref_n = min(STEP3_DRAM_CAPTURES, key=lambda n: abs(n - N))
         ref_bytes, ref_loads = STEP3_DRAM_CAPTURES[ref_n]
         traffic = ref_bytes * tile_pair_loads / ref_loads
+        aux = args.q_shift != 0.0 or args.theta != 12.0
         line = {
             "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": W, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
+            "dtype": "bf16",
+            "data": f"synthetic, AUXILIARY distribution (q_shift {args.q_shift}, theta {args.theta})" if aux else "synthetic",
             "config": {"workload": f"anchor_attn layer, seq {N}, {H}q/{HKV}kv heads, head_dim {D}, block {BLOCK}, "
                                    f"step {STEP}, theta {THETA}",
                        "parallelism": (f"heads by KV group over {W} GPU(s), " +
@@ -354,6 +358,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=131072)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--q-shift", type=float, default=0.0,
+                    help="auxiliary distribution: add this to Q before the stripe step (sparse selection); "
+                         "not the benchmark configuration")
+    ap.add_argument("--theta", type=float, default=THETA, help="auxiliary runs only; the benchmark uses 12")
     ap.add_argument("--exchange", default="push", choices=["push", "all_gather"],
                     help="how the head outputs reach every rank when N > 1")
     args = ap.parse_args()
