@@ -178,6 +178,13 @@ def test_reference_layout_export(lib):
         for b in range(3):
             c = int(counts[0, h, b, 0])
             assert torch.equal(coords[0, h, b, :c].cpu(), lists[0][h][b])
+    # the host-side sum of the counts (numerator of the reference's sparsity ratio)
+    import ctypes
+    total = ctypes.c_int64(-1)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.aa_total_selected(ctypes.byref(call.params), stream, ctypes.byref(total)) == 0
+    assert total.value == int(counts.sum())
+    assert abs(float(call.ratio()) - total.value / ((H * N * N / 2048) // 2)) < 1e-6
 
 
 def test_full_size_sampled_blocks_and_properties(lib):
