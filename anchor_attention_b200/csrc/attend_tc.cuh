@@ -89,15 +89,12 @@ struct TcArgs {
 #ifndef AA_ORDER_KV_MAJOR
 #define AA_ORDER_KV_MAJOR 1
 #endif
-#ifndef AA_SPLIT_P
-#define AA_SPLIT_P 1
-#endif
 #ifndef AA_TMA_ROWS
 #define AA_TMA_ROWS 32
 #endif
 constexpr int kTmaRows = AA_TMA_ROWS;       // rows of a gathered tile fetched by TMA row gathers (multiple of 4)
 constexpr int kPolyShare = AA_POLY_SHARE;   // element pairs out of every 4 whose exp2 is a polynomial (0..4)
-constexpr bool kSplitP = AA_SPLIT_P != 0;   // signal the first half of P early so that P V can start on it
+constexpr int kPParts = 2;                  // P is handed to the MMA warp in two halves
 
 // 2^x for a pair of fp32 values on the FMA pipe: x = n + f with n = floor(x);
 // 2^f from a cubic (max relative error 8.6e-5, far below the bf16 rounding of P),
@@ -136,12 +133,12 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, u
 }
 
 // What the softmax warps need to know about their CTA: where the tiles and barriers are.
-// q_full / p_ready / p_ready2 are arrived on, s_full / o_done are waited on.
+// q_full / p_part are arrived on, s_full / o_done are waited on.
 struct SoftmaxCtx {
     uint8_t* smem;
     uint32_t tmem_base;
     volatile int* abort_flag;
-    uint32_t q_full[2], s_full[2], p_ready[2], p_ready2[2], o_done[2];
+    uint32_t q_full[2], s_full[2], o_done[2], p_part[2][4];
     int pair, z, h, hz, ntiles, n_init, local_start, count;
 };
 
@@ -158,7 +155,9 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     (void)n_init; (void)local_start; (void)count;
     const int j = warp >> 2;
     const uint32_t q_full_j = cx.q_full[j], s_full_j = cx.s_full[j], o_done_j = cx.o_done[j];
-    const uint32_t p_ready_j = cx.p_ready[j], p_ready2_j = cx.p_ready2[j];
+    uint32_t p_part_j[kPParts];
+#pragma unroll
+    for (int q = 0; q < kPParts; ++q) p_part_j[q] = cx.p_part[j][q];
     const int r = tid & 127;
     const int qb = 2 * pair + j;
     const int row_g = qb * kTile + r;
@@ -288,28 +287,37 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         }
         float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         const float2 neg_ref = make_float2(-m_ref, -m_ref);
+        // P goes to the MMA warp in two halves of 64 key columns (32 packed tensor-memory columns),
+        // each enough for four k-steps of P V, so that P V starts while the second half is computed.
+        // (Four parts, or signalling the first half later so that its store completes in the shadow of
+        // the second half's arithmetic, measured slower or equal.)
+        auto exp_pairs = [&](uint32_t (&pk)[32], int c, int i_begin, int i_end) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            uint32_t pk[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = i_begin; i < i_end; ++i) {
                 const int e = c * 64 + 2 * i;
                 const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
                                                         __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
                 // kPolyShare of every 4 element pairs take the polynomial on the FMA pipe,
-                // the others the MUFU unit: both pipes are busy
+                // the others the MUFU unit
                 const float2 p = ((i & 3) < kPolyShare) ? exp2_poly2(d) : make_float2(fast_exp2(d.x), fast_exp2(d.y));
                 rs[i & 3] = __fadd2_rn(rs[i & 3], p);
                 pk[i] = pack_bf16x2(p.x, p.y);
             }
-            tmem_st32(tS + c * 32, pk);
-            // the first 64 columns of P are enough for the first four k-steps of P V
-            if (kSplitP || c == 1) {
-                tmem_wait_st();
-                tcgen05_fence_before();
-                mbar_arrive((kSplitP && c == 1) ? p_ready2_j : p_ready_j);
-            }
-        }
+        };
+        auto signal = [&](uint32_t bar) {
+            tmem_wait_st();
+            tcgen05_fence_before();
+            // one arrival per warp: 128 arrivals on one barrier would queue up behind each other
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(bar);
+        };
+        uint32_t pk0[32], pk1[32];
+        exp_pairs(pk0, 0, 0, 32);
+        tmem_st32(tS, pk0);
+        signal(p_part_j[0]);
+        exp_pairs(pk1, 1, 0, 32);
+        tmem_st32(tS + 32, pk1);
+        signal(p_part_j[1]);
         const float2 rsum = __fadd2_rn(__fadd2_rn(rs[0], rs[1]), __fadd2_rn(rs[2], rs[3]));
         l += rsum.x + rsum.y;
     }
@@ -413,12 +421,11 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     auto kv_empty = [&](int i) { return bars + 40u + 8u * i; };
     auto q_full = [&](int j) { return bars + 80u + 8u * j; };
     auto s_full = [&](int j) { return bars + 96u + 8u * j; };
-    auto p_ready = [&](int j) { return bars + 112u + 8u * j; };
-    auto o_done = [&](int j) { return bars + 128u + 8u * j; };
-    auto p_ready2 = [&](int j) { return bars + 144u + 8u * j; };
-    const uint32_t tmem_slot_u = bars + 160u;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemQ + kSmemRing + 160);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 164);
+    auto o_done = [&](int j) { return bars + 112u + 8u * j; };
+    auto p_part = [&](int j, int q) { return bars + 128u + 8u * (4 * j + q); };
+    const uint32_t tmem_slot_u = bars + 192u;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kSmemQ + kSmemRing + 192);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 196);
 
     // ---- which work item ----
     const int BH = a.B * a.H;
@@ -468,8 +475,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         for (int j = 0; j < 2; ++j) {
             mbar_init(q_full(j), 128);
             mbar_init(s_full(j), 1);
-            mbar_init(p_ready(j), 128);
-            mbar_init(p_ready2(j), 128);
+            for (int q = 0; q < kPParts; ++q) mbar_init(p_part(j, q), 4);       // one arrival per softmax warp
             mbar_init(o_done(j), 1);
         }
         *abort_flag = 0;
@@ -494,8 +500,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         for (int jj = 0; jj < 2; ++jj) {
             sc.q_full[jj] = q_full(jj);
             sc.s_full[jj] = s_full(jj);
-            sc.p_ready[jj] = p_ready(jj);
-            sc.p_ready2[jj] = p_ready2(jj);
+            for (int q = 0; q < 4; ++q) sc.p_part[jj][q] = p_part(jj, q);
             sc.o_done[jj] = o_done(jj);
         }
         sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
@@ -529,7 +534,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             auto issue_pv = [&](int j, uint32_t vaddr, bool acc, int ks0) {
                 const uint32_t v_lo = lo_mnmajor(vaddr);
 #pragma unroll
-                for (int ks = ks0; ks < ks0 + 4; ++ks)
+                for (int ks = ks0; ks < ks0 + 8 / kPParts; ++ks)
                     if (issuer)
                         mma_ts(tmem_base + 256u + (uint32_t)j * 128u, tmem_base + (uint32_t)j * 128u + (uint32_t)ks * 8u,
                                desc(v_lo + (uint32_t)ks * (2048u >> 4)), kIdescPV, (ks > 0) || acc);
@@ -553,16 +558,13 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 if (!ok) break;
                 fence_proxy_async();
                 for (int j = 0; j < 2 && ok; ++j) {
-                    ok = wait_all(p_ready(j), t & 1);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe), 0);
-                    if (kSplitP) {
-                        ok = wait_all(p_ready2(j), t & 1);
+                    for (int q = 0; q < kPParts && ok; ++q) {
+                        ok = wait_all(p_part(j, q), t & 1);
                         if (!ok) break;
                         tcgen05_fence_after();
+                        issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe) || q > 0, q * (8 / kPParts));
                     }
-                    issue_pv(j, slot_addr(nv), true, 4);
+                    if (!ok) break;
                     if (j == 1) commit_if(issuer, kv_empty(nv % kStages));
                     if (t + 1 < ntiles) {
                         if (j == 0) {
