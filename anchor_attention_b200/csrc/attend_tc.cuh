@@ -169,7 +169,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     // Q tile: load, scale, round, store in the K-major 128B-swizzled layout the MMA reads
     {
         const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
-        const float c1 = bf16_round(a.sm_scale), c2 = bf16_round(kLog2e);
+        const __nv_bfloat162 c1b = __float2bfloat162_rn(a.sm_scale), c2b = __float2bfloat162_rn(kLog2e);
         uint8_t* qs = smem + j * kTileBytes;
         // all sixteen loads of the thread are issued before the first one is used
         uint4 raws[16];
@@ -186,15 +186,16 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
             __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float2 f = __bfloat1622float2(p2[e]);
                 if (MODE == kWindow) {
-                    f.x = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.x, c1)), c2));
-                    f.y = bf16_round(__fmul_rn(bf16_round(__fmul_rn(f.y, c1)), c2));
+                    // bf16(bf16(q * c1) * c2) with bf16 constants: a product of two bf16 values is exact
+                    // in fp32, so the packed bf16 multiply (one rounding) gives the same bits
+                    p2[e] = __hmul2(__hmul2(p2[e], c1b), c2b);
                 } else {
+                    float2 f = __bfloat1622float2(p2[e]);
                     f.x = __fmul_rn(__fmul_rn(f.x, a.sm_scale), kLog2e);
                     f.y = __fmul_rn(__fmul_rn(f.y, a.sm_scale), kLog2e);
+                    p2[e] = __floats2bfloat162_rn(f.x, f.y);
                 }
-                p2[e] = __floats2bfloat162_rn(f.x, f.y);
             }
             *reinterpret_cast<uint4*>(qs + sw_off(rr, ch)) = raw;
         }
@@ -329,21 +330,42 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         tcgen05_fence_after();
     }
     if (MODE == kWindow) {
-        if (ok) {
+        // All 128 threads of the tile get here; they first agree that none of them gave up.  The fp32
+        // accumulator rows (512 bytes each) are staged in shared memory (the tile's query buffer, which
+        // no MMA reads any more), 64 columns at a time, and written out as whole 256-byte pieces by
+        // consecutive threads.
+        const bool all_ok = bar_and(1 + j, 128, ok);
+        if (all_ok) {
             const float sc = fast_exp2(m_ref - m_true);
             a.M[srow] = m_true;
             a.L[srow] = l * sc;
-            float4* dst = reinterpret_cast<float4*>(a.Acc + srow * kD);
+            uint8_t* stage = smem + j * kTileBytes;
+            float* tile_acc = a.Acc + ((int64_t)hz * a.N + (int64_t)qb * kTile) * kD;
+            const int ch = r & 15;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tO + c * 32, v);
-                tmem_wait_ld();
+            for (int hcol = 0; hcol < 2; ++hcol) {
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tO + hcol * 64 + c * 32, v);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    dst[c * 8 + i] = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
-                                                 __uint_as_float(v[4 * i + 2]) * sc,
-                                                 __uint_as_float(v[4 * i + 3]) * sc);
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 x = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
+                                                     __uint_as_float(v[4 * i + 2]) * sc,
+                                                     __uint_as_float(v[4 * i + 3]) * sc);
+                        // row r, 16-byte chunk c*8+i of this 256-byte half row, at chunk slot (chunk ^ (r & 7))
+                        *reinterpret_cast<float4*>(stage + r * kRowBytes + (((c * 8 + i) ^ (r & 7)) << 4)) = x;
+                    }
+                }
+                bar_sync(1 + j, 128);
+#pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                    const int row = it * 8 + (r >> 4);
+                    const float4 x = *reinterpret_cast<const float4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
+                    *reinterpret_cast<float4*>(tile_acc + (int64_t)row * kD + hcol * 64 + ch * 4) = x;
+                }
+                bar_sync(1 + j, 128);
             }
         }
     } else {
