@@ -377,6 +377,15 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         if (all_ok) {
             uint8_t* stage = smem + j * kTileBytes;
             const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+            // acc / l, correctly rounded: one IEEE reciprocal of l per row, then the quotient estimate
+            // acc * (1/l) corrected once with the exact remainder (two fused multiply-adds).  Equals the
+            // IEEE quotient for normal operands, at a third of the instructions of a division.
+            const float rl = __frcp_rn(l);
+            auto div_l = [&](float x) {
+                const float q0 = __fmul_rn(x, rl);
+                const float rem = __fmaf_rn(-q0, l, x);
+                return __fmaf_rn(rem, rl, q0);
+            };
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t v[32];
@@ -396,10 +405,10 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     uint4 o4;
-                    o4.x = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i]), l), __fdiv_rn(__uint_as_float(v[8 * i + 1]), l));
-                    o4.y = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 2]), l), __fdiv_rn(__uint_as_float(v[8 * i + 3]), l));
-                    o4.z = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 4]), l), __fdiv_rn(__uint_as_float(v[8 * i + 5]), l));
-                    o4.w = pack_bf16x2(__fdiv_rn(__uint_as_float(v[8 * i + 6]), l), __fdiv_rn(__uint_as_float(v[8 * i + 7]), l));
+                    o4.x = pack_bf16x2(div_l(__uint_as_float(v[8 * i])), div_l(__uint_as_float(v[8 * i + 1])));
+                    o4.y = pack_bf16x2(div_l(__uint_as_float(v[8 * i + 2])), div_l(__uint_as_float(v[8 * i + 3])));
+                    o4.z = pack_bf16x2(div_l(__uint_as_float(v[8 * i + 4])), div_l(__uint_as_float(v[8 * i + 5])));
+                    o4.w = pack_bf16x2(div_l(__uint_as_float(v[8 * i + 6])), div_l(__uint_as_float(v[8 * i + 7])));
                     // row r, 16-byte chunk c*4+i, stored at chunk slot (chunk ^ (r & 7)): conflict-free
                     *reinterpret_cast<uint4*>(stage + r * kRowBytes + (((c * 4 + i) ^ (r & 7)) << 4)) = o4;
                 }
