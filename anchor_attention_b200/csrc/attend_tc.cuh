@@ -167,7 +167,8 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)j * 128u;
 
     // Q tile: load, scale, round, store in the K-major 128B-swizzled layout the MMA reads
-    {
+    // (not needed when there is no key tile to multiply it with)
+    if (ntiles > 0) {
         const __nv_bfloat16* qbase = a.q.ptr + z * a.q.sb + h * a.q.sh + (int64_t)qb * kTile * a.q.sn;
         const __nv_bfloat162 c1b = __float2bfloat162_rn(a.sm_scale), c2b = __float2bfloat162_rn(kLog2e);
         uint8_t* qs = smem + j * kTileBytes;
