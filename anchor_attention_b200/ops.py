@@ -13,6 +13,7 @@ PyTorch is used for device memory and the current stream only.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -23,6 +24,7 @@ __all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "Anc
            "launches_per_forward"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_NVTX = os.environ.get("ANCHOR_ATTN_NVTX", "0") == "1"
 
 
 def _workspace(device: torch.device, stream_id: int, nbytes: int) -> torch.Tensor:
@@ -96,24 +98,37 @@ class AnchorAttnCall:
         self._lib = lib
 
     # ---- launches -------------------------------------------------------
-    def _call(self, fn):
-        with torch.cuda.device(self.Q.device):
-            rc = fn(ctypes.byref(self.params), ctypes.c_void_p(self.stream.cuda_stream))
+    def _call(self, fn, label=None):
+        """Enqueue one entry point; with ANCHOR_ATTN_NVTX=1 the launch is wrapped in an NVTX
+        range named after the step, so that a timeline shows the three steps of every call."""
+        nvtx = label is not None and _NVTX
+        if nvtx:
+            torch.cuda.nvtx.range_push(label)
+        try:
+            with torch.cuda.device(self.Q.device):
+                rc = fn(ctypes.byref(self.params), ctypes.c_void_p(self.stream.cuda_stream))
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         if rc != _lib.AA_OK:
             raise RuntimeError(f"anchor_attn: {_lib.error_text(rc)}")
 
     def run(self):
+        if _NVTX:                      # one range per step instead of one for the whole call
+            self.step1()
+            self.step2()
+            return self.step3()
         self._call(self._lib.aa_forward)
         return self.out
 
     def step1(self):
-        self._call(self._lib.aa_step1_anchor)
+        self._call(self._lib.aa_step1_anchor, "anchor_attn.step1_anchor")
 
     def step2(self):
-        self._call(self._lib.aa_step2_stripes)
+        self._call(self._lib.aa_step2_stripes, "anchor_attn.step2_stripes")
 
     def step3(self):
-        self._call(self._lib.aa_step3_sparse)
+        self._call(self._lib.aa_step3_sparse, "anchor_attn.step3_sparse")
         return self.out
 
     def step3_push(self, peer_ptrs):
