@@ -124,3 +124,40 @@ def test_without_anchor_alias_exists():
     sig = inspect.signature(anchor_attn_without_anchor)
     assert list(sig.parameters) == ["Q", "K", "V", "sm_scale", "block_size", "step", "difference"]
     assert sig.parameters["difference"].default == 12 and sig.parameters["block_size"].default == 128
+
+
+def test_ctypes_mirrors_match_the_header(tmp_path):
+    """Sizes and field offsets of the ctypes structures equal what a C compiler makes of the
+    header (a drifted mirror would pass wrong pointers silently)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    checks = {
+        "aa_params_t": (_lib.AAParams, ["B", "D", "theta", "sm_scale", "q", "out", "q_stride_b", "o_stride_n",
+                                        "workspace", "workspace_bytes"]),
+        "aa_workspace_layout_t": (_lib.AALayout, ["m_off", "ids_off", "status_off", "total_bytes", "ids_per_head"]),
+        "aa_stripes_static_args_t": (_lib.AAStripesStaticArgs, ["B", "theta", "q", "k_stride_n", "anchors", "ids"]),
+        "aa_push_t": (_lib.AAPush, ["n_peers", "out"]),
+    }
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{os.path.abspath(HEADER)}"', "int main(void) {"]
+    for cname, (_, fields) in checks.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for f in fields:
+            lines.append(f'  printf("{cname} {f} %zu\\n", offsetof({cname}, {f}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = 0
+    for line in out.splitlines():
+        cname, field, value = line.split()
+        ct = checks[cname][0]
+        want = ctypes.sizeof(ct) if field == "size" else getattr(ct, field).offset
+        assert int(value) == want, f"{cname}.{field}: header {value}, ctypes {want}"
+        seen += 1
+    assert seen == sum(len(f) + 1 for _, f in checks.values())
+    assert _lib.MAX_PEERS == 8 and _lib.STATIC_SCRATCH_BYTES == 8 << 20
