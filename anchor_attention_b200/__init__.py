@@ -2,6 +2,7 @@
 backed by hand-written sm_100a CUDA kernels behind a C ABI."""
 from .ops import (AnchorAttnCall, anchor_attn, anchor_attn_host, anchor_attn_without_anchor,
                   launches_per_forward)
+from .block_sparse import block_sparse_attention
 
 __all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
-           "launches_per_forward"]
+           "launches_per_forward", "block_sparse_attention"]

@@ -17,7 +17,8 @@ EXPORTS = [
     "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
     "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
-    "aa_selftest_wait_timeout",
+    "aa_selftest_wait_timeout", "aa_block_sparse_workspace_bytes", "aa_block_sparse_attend",
+    "aa_block_sparse_check_status",
 ]
 MAX_PEERS = 8
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -57,6 +58,22 @@ class AAStripesStaticArgs(ctypes.Structure):
     ]
 
 
+class AABlockSparse(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32),
+        ("N", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("max_blocks", ctypes.c_int32),
+        ("sm_scale", ctypes.c_double),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("q_stride_b", ctypes.c_int64), ("q_stride_h", ctypes.c_int64), ("q_stride_n", ctypes.c_int64),
+        ("k_stride_b", ctypes.c_int64), ("k_stride_h", ctypes.c_int64), ("k_stride_n", ctypes.c_int64),
+        ("v_stride_b", ctypes.c_int64), ("v_stride_h", ctypes.c_int64), ("v_stride_n", ctypes.c_int64),
+        ("o_stride_b", ctypes.c_int64), ("o_stride_h", ctypes.c_int64), ("o_stride_n", ctypes.c_int64),
+        ("block_index", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+    ]
+
+
 class AAPush(ctypes.Structure):
     _fields_ = [("n_peers", ctypes.c_int32), ("out", ctypes.c_void_p * MAX_PEERS)]
 
@@ -87,6 +104,12 @@ def load():
     lib.aa_step2_stripes_static.restype = ctypes.c_int
     lib.aa_step3_sparse_push.argtypes = [P, ctypes.POINTER(AAPush), ctypes.c_void_p]
     lib.aa_step3_sparse_push.restype = ctypes.c_int
+    PB = ctypes.POINTER(AABlockSparse)
+    lib.aa_block_sparse_workspace_bytes.argtypes = [PB, ctypes.POINTER(ctypes.c_size_t)]
+    lib.aa_block_sparse_workspace_bytes.restype = ctypes.c_int
+    for name in ("aa_block_sparse_attend", "aa_block_sparse_check_status"):
+        getattr(lib, name).argtypes = [PB, ctypes.c_void_p]
+        getattr(lib, name).restype = ctypes.c_int
     lib.aa_total_selected.argtypes = [P, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
     lib.aa_strerror.argtypes = [ctypes.c_int]
     lib.aa_strerror.restype = ctypes.c_char_p

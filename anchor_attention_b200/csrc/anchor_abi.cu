@@ -10,6 +10,7 @@
 #include <string.h>
 
 #include "attend_tc.cuh"
+#include "block_list.cuh"
 #include "common.cuh"
 #include "score_tc.cuh"
 #include "stripe.cuh"
@@ -198,8 +199,8 @@ int make_gather_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, i
 
 template <int MODE>
 int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st,
-                     const aa_push_t* push = nullptr) {
-    static thread_local int configured_dev[2] = {-1, -1};
+                     const aa_push_t* push = nullptr, int list_stride = 0) {
+    static thread_local int configured_dev[3] = {-1, -1, -1};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
@@ -213,6 +214,7 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     ta.a = attend_args(p, lay);
     ta.status = ws_ptr<int32_t>(p, lay.status_off);
     ta.n_peers = 0;
+    ta.list_stride = list_stride;
     for (int i = 0; i < aa::tc::kMaxPeers; ++i) ta.peers[i] = nullptr;
     if (push) {
         ta.n_peers = push->n_peers;
@@ -237,7 +239,9 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / (2 * aa::tc::kTile)));
     aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, ta);
     e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)" : "launch step3 (tc)");
+    if (e != cudaSuccess)
+        return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)"
+                                                : (MODE == aa::kStripe ? "launch step3 (tc)" : "launch block-sparse (tc)"));
     return AA_OK;
 }
 
@@ -584,6 +588,127 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     return AA_OK;
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// The block-granular comparator (see the header): merged tile lists in the caller's
+// workspace, then the attention kernel in its block mode.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct BlockSparseLayout {
+    size_t lists_off, counts_off, status_off, total_bytes;
+    int npairs, list_stride;
+};
+
+int block_sparse_layout(const aa_block_sparse_t* a, BlockSparseLayout* lay) {
+    if (!a) return AA_ERR_NULL;
+    if (a->B <= 0 || a->H <= 0 || a->Hkv <= 0 || a->N <= 0 || a->H % a->Hkv != 0 || a->max_blocks <= 0)
+        return AA_ERR_SHAPE;
+    if (a->D != 128) return AA_ERR_HEAD_DIM;
+    if (a->N % (2 * aa::tc::kTile) != 0) return AA_ERR_SEQ;
+    if (a->dtype != AA_BF16) return AA_ERR_DTYPE;
+    if ((int64_t)a->N * a->H * a->B > (int64_t)1 << 40 || a->N / aa::tc::kTile > (int)aa::kBlockIdMask)
+        return AA_ERR_TOO_LARGE;
+    const size_t BH = (size_t)a->B * a->H;
+    lay->npairs = a->N / (2 * aa::tc::kTile);
+    // a pair's merged list holds at most the entries both query blocks read
+    const int64_t stride = 2 * (int64_t)(a->max_blocks < a->N / aa::tc::kTile ? a->max_blocks : a->N / aa::tc::kTile);
+    lay->list_stride = (int)stride;
+    size_t off = 0;
+    lay->lists_off = off;   off = align_up(off + BH * lay->npairs * (size_t)stride * sizeof(int32_t));
+    lay->counts_off = off;  off = align_up(off + BH * lay->npairs * sizeof(int32_t));
+    lay->status_off = off;  off = align_up(off + 4 * sizeof(int32_t));
+    lay->total_bytes = off;
+    return AA_OK;
+}
+
+int block_sparse_check(const aa_block_sparse_t* a, BlockSparseLayout* lay) {
+    int rc = block_sparse_layout(a, lay);
+    if (rc) return rc;
+    if (!a->q || !a->k || !a->v || !a->out || !a->block_index) return AA_ERR_NULL;
+    const int64_t st[] = {a->q_stride_b, a->q_stride_h, a->q_stride_n, a->k_stride_b, a->k_stride_h, a->k_stride_n,
+                          a->v_stride_b, a->v_stride_h, a->v_stride_n, a->o_stride_b, a->o_stride_h, a->o_stride_n};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return AA_ERR_STRIDE;
+    if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15) return AA_ERR_STRIDE;
+    if (!a->workspace || ((uintptr_t)a->workspace & 255) || a->workspace_bytes < lay->total_bytes)
+        return AA_ERR_WORKSPACE;
+    return AA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int aa_block_sparse_workspace_bytes(const aa_block_sparse_t* a, size_t* bytes) {
+    if (!bytes) return AA_ERR_NULL;
+    BlockSparseLayout lay;
+    int rc = block_sparse_layout(a, &lay);
+    if (rc) return rc;
+    *bytes = lay.total_bytes;
+    return AA_OK;
+}
+
+int aa_block_sparse_attend(const aa_block_sparse_t* a, void* stream) {
+    BlockSparseLayout bl;
+    int rc = block_sparse_check(a, &bl);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    int32_t* status = reinterpret_cast<int32_t*>(ws + bl.status_off);
+    cudaError_t e = cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
+    const int BH = a->B * a->H, items = BH * bl.npairs;
+    aa::merge_block_lists_kernel<<<(items + 127) / 128, 128, 0, st>>>(
+        a->block_index, BH, a->N / aa::tc::kTile, a->max_blocks, reinterpret_cast<int32_t*>(ws + bl.lists_off),
+        reinterpret_cast<int32_t*>(ws + bl.counts_off), bl.list_stride, status + 1);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch merge_block_lists");
+
+    // the attention kernel takes the operator's argument block: fill in what the block mode reads
+    aa_params_t p;
+    memset(&p, 0, sizeof(p));
+    p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.N = a->N; p.D = a->D;
+    p.block_size = 128; p.step = 16; p.dtype = a->dtype;
+    p.sm_scale = a->sm_scale;
+    p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out;
+    p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h; p.q_stride_n = a->q_stride_n;
+    p.k_stride_b = a->k_stride_b; p.k_stride_h = a->k_stride_h; p.k_stride_n = a->k_stride_n;
+    p.v_stride_b = a->v_stride_b; p.v_stride_h = a->v_stride_h; p.v_stride_n = a->v_stride_n;
+    p.o_stride_b = a->o_stride_b; p.o_stride_h = a->o_stride_h; p.o_stride_n = a->o_stride_n;
+    p.workspace = a->workspace;
+    p.workspace_bytes = a->workspace_bytes;
+    aa_workspace_layout_t lay;
+    memset(&lay, 0, sizeof(lay));
+    lay.counts_off = bl.counts_off;
+    lay.ids_off = bl.lists_off;
+    lay.status_off = bl.status_off;
+    lay.ids_per_head = (int64_t)bl.npairs * bl.list_stride;
+    lay.total_bytes = bl.total_bytes;
+    return launch_attend_tc<aa::kBlock>(&p, lay, st, nullptr, bl.list_stride);
+}
+
+int aa_block_sparse_check_status(const aa_block_sparse_t* a, void* stream) {
+    BlockSparseLayout bl;
+    int rc = block_sparse_check(a, &bl);
+    if (rc) return rc;
+    int32_t status[4] = {0, 0, 0, 0};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(status, static_cast<uint8_t*>(a->workspace) + bl.status_off, sizeof(status),
+                                    cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    if (status[0] != 0) return AA_ERR_DEVICE_TIMEOUT;
+    if (status[1] != 0) return AA_ERR_UNSORTED;
+    return AA_OK;
+}
+
+}  // extern "C"
+
+extern "C" {
+
 const char* aa_strerror(int code) {
     switch (code) {
         case AA_OK: return "ok";
@@ -599,6 +724,7 @@ const char* aa_strerror(int code) {
         case AA_ERR_CUDA: return "CUDA call failed";
         case AA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
         case AA_ERR_TOO_LARGE: return "problem too large for this entry point";
+        case AA_ERR_UNSORTED: return "a block list is not in ascending order";
         default: return "unknown error";
     }
 }

@@ -11,6 +11,11 @@
 //   kStripe  (step 3)  tiles of 128 ids from the big block's id list; state starts
 //            from step 1's (M, L, Acc); slots past the count masked to -inf;
 //            writes bf16(acc / l).  Reference: anchor_attn/src/ops/anchor_attn_v4.py:7-105.
+//   kBlock   (block-granular comparator)  whole 128-row key blocks from the merged block list
+//            of the CTA's two query tiles; an entry says which of the two tiles attends it (the
+//            other one hands the MMA warp a zero P); -inf causal mask on a tile's own block;
+//            state starts empty; writes bf16(acc / l).
+//            Reference: anchor_attn/src/ops/block_sparse_flash_attention_v2.py:10-110.
 //
 // Warp roles (384 threads):
 //   warps 0-3   softmax of tile A: thread r owns query row r = tensor-memory lane r
@@ -75,6 +80,7 @@ struct TcArgs {
     int kpos_n, kpos_h, kpos_b;      // which tensor-map coordinate (1..3 -> 0..2) carries n / head / batch
     int vpos_n, vpos_h, vpos_b;
     int k_gather, v_gather;          // 1: the 2-D row-gather tensor map of K / V is usable
+    int list_stride;                 // kBlock only: entries reserved per query-tile pair in a.ids
     int n_peers;                     // step 3 only: > 0 -> write the output to peers[0 .. n_peers) instead of a.out
     __nv_bfloat16* peers[kMaxPeers]; // same element offsets and strides as a.out; may be other GPUs' memory
     int32_t* status;
@@ -140,6 +146,7 @@ struct SoftmaxCtx {
     volatile int* abort_flag;
     uint32_t q_full[2], s_full[2], o_done[2], p_part[2][4];
     int pair, z, h, hz, ntiles, n_init, local_start, count;
+    const int32_t* list;             // kBlock only: the pair's tile list
 };
 
 // The softmax role of warps 0-7 (see the file header): thread r of tile j owns query row r.
@@ -191,6 +198,11 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                     // bf16(bf16(q * c1) * c2) with bf16 constants: a product of two bf16 values is exact
                     // in fp32, so the packed bf16 multiply (one rounding) gives the same bits
                     p2[e] = __hmul2(__hmul2(p2[e], c1b), c2b);
+                } else if (MODE == kBlock) {
+                    // bf16(q * (sm_scale * log2e)): the constants are multiplied first
+                    const float qk = __fmul_rn(a.sm_scale, kLog2e);
+                    float2 f = __bfloat1622float2(p2[e]);
+                    p2[e] = __floats2bfloat162_rn(__fmul_rn(f.x, qk), __fmul_rn(f.y, qk));
                 } else {
                     float2 f = __bfloat1622float2(p2[e]);
                     f.x = __fmul_rn(__fmul_rn(f.x, a.sm_scale), kLog2e);
@@ -230,12 +242,33 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         l = 0.f;
     }
 
+    auto signal = [&](uint32_t bar) {
+        tmem_wait_st();
+        tcgen05_fence_before();
+        // one arrival per warp: 128 arrivals on one barrier would queue up behind each other
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar);
+    };
+    uint32_t entry_next = (MODE == kBlock && ntiles > 0) ? (uint32_t)cx.list[0] : 0u;
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
+        const uint32_t entry = entry_next;
+        if (MODE == kBlock && t + 1 < ntiles) entry_next = (uint32_t)cx.list[t + 1];
         ok = mbar_wait(s_full_j, t & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
+        if (MODE == kBlock && !((entry >> (kBlockFlagShift + j)) & 1u)) {
+            // the block belongs to the other query tile only: P = 0 leaves the accumulator as it is
+            uint32_t zero[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) zero[i] = 0u;
+            tmem_st32(tS, zero);
+            signal(p_part_j[0]);
+            tmem_st32(tS + 32, zero);
+            signal(p_part_j[1]);
+            continue;
+        }
         uint32_t sv[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
@@ -250,6 +283,14 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                     for (int i = 0; i < 32; ++i)
                         if (col0 + c * 32 + i > row_g)
                             sv[c][i] = __float_as_uint(__uint_as_float(sv[c][i]) + -1e6f);
+            }
+        } else if (MODE == kBlock) {
+            if ((int)(entry & kBlockIdMask) == qb) {      // the tile's own block: keys after the query row
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i > r) sv[c][i] = __float_as_uint(-INFINITY);
             }
         } else {
             const int valid = count - t * kTile;
@@ -273,7 +314,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         // move the exponent reference only when some row of the warp needs it
         if (__any_sync(0xffffffffu, m_true > m_ref + kRescaleThreshold)) {
             const float alpha = fast_exp2(m_ref - m_true);
-            if (!(MODE == kWindow && t == 0)) {
+            if (!(MODE != kStripe && t == 0)) {       // nothing accumulated yet when the state starts empty
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
                     uint32_t v[32];
@@ -305,13 +346,6 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 rs[i & 3] = __fadd2_rn(rs[i & 3], p);
                 pk[i] = pack_bf16x2(p.x, p.y);
             }
-        };
-        auto signal = [&](uint32_t bar) {
-            tmem_wait_st();
-            tcgen05_fence_before();
-            // one arrival per warp: 128 arrivals on one barrier would queue up behind each other
-            __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(bar);
         };
         uint32_t pk0[32], pk1[32];
         exp_pairs(pk0, 0, 0, 32);
@@ -381,6 +415,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
             // acc / l, correctly rounded: one IEEE reciprocal of l per row, then the quotient estimate
             // acc * (1/l) corrected once with the exact remainder (two fused multiply-adds).  Equals the
             // IEEE quotient for normal operands, at a third of the instructions of a division.
+            if (MODE == kBlock && ntiles == 0) l = 1.f;          // an empty list: zeros (the lists are never empty)
             const float rl = __frcp_rn(l);
             auto div_l = [&](float x) {
                 const float q0 = __fmul_rn(x, rl);
@@ -393,6 +428,9 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 if (ntiles > 0) {
                     tmem_ld32(tO + c * 32, v);
                     tmem_wait_ld();
+                } else if (MODE == kBlock) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -491,6 +529,10 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         local_start = max(b * G, init_end);
         n_init = init_end / kTile;
         ntiles = n_init + (end - local_start) / kTile;
+    } else if (MODE == kBlock) {
+        count = a.counts[(int64_t)hz * npairs + pair];          // entries of the pair's merged tile list
+        ntiles = count;
+        idp = a.ids + (int64_t)hz * a.ids_per_head + (int64_t)pair * ta.list_stride;
     } else {
         count = a.counts[(int64_t)hz * NB + b];
         ntiles = (count + kTile - 1) / kTile;
@@ -537,6 +579,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         }
         sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
         sc.ntiles = ntiles; sc.n_init = n_init; sc.local_start = local_start; sc.count = count;
+        sc.list = idp;
         softmax_role<MODE>(ta, sc, tid);
     } else {
         setmaxnreg_dec<AA_OTHER_REGS>();
@@ -638,6 +681,8 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 bool run = true;     // 128 consecutive rows -> one TMA tile
                 if (MODE == kWindow) {
                     row0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
+                } else if (MODE == kBlock) {
+                    row0 = (int)((uint32_t)idp[t] & kBlockIdMask) * kTile;
                 } else {
                     const int s0 = t * kTile;
                     run = false;

@@ -15,8 +15,13 @@ struct TensorView {          // one [B, heads, N, 128] bf16 tensor, strides in e
     int64_t sb, sh, sn;
 };
 
-// Which of the two attention passes a kernel instance runs.
-enum AttendMode { kWindow = 0, kStripe = 1 };
+// Which attention pass a kernel instance runs: the operator's two passes, or the
+// block-granular comparator (whole 128-row key blocks from a per-query-block list).
+enum AttendMode { kWindow = 0, kStripe = 1, kBlock = 2 };
+
+// kBlock tile-list entries: key block index in the low bits, one flag per query tile of the pair.
+constexpr uint32_t kBlockIdMask = 0x00FFFFFFu;
+constexpr int kBlockFlagShift = 30;       // bit 30: first query tile attends the block, bit 31: second
 
 // Arguments shared by both passes: the tensors, the inter-kernel state in the
 // workspace and the problem sizes.

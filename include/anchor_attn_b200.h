@@ -36,7 +36,8 @@ enum {
     AA_ERR_DTYPE = -9,         /* dtype is not AA_BF16                               */
     AA_ERR_CUDA = -10,         /* a CUDA runtime/driver call failed (see aa_last_cuda_error) */
     AA_ERR_DEVICE_TIMEOUT = -11,/* a bounded device-side wait gave up (status word)  */
-    AA_ERR_TOO_LARGE = -12     /* size beyond what an entry point supports           */
+    AA_ERR_TOO_LARGE = -12,    /* size beyond what an entry point supports           */
+    AA_ERR_UNSORTED = -13      /* a key-block list of the comparator is not ascending */
 };
 
 enum { AA_BF16 = 0 };
@@ -196,6 +197,47 @@ typedef struct aa_stripes_static_args {
 } aa_stripes_static_args_t;
 
 int aa_step2_stripes_static(const aa_stripes_static_args_t *args, void *stream);
+
+/*
+ * The block-granular comparator the reference measures anchor attention against:
+ * block-sparse flash attention in which every 128-row query block attends a list of whole
+ * 128-row key blocks.  Replaces _triton_block_sparse_attention and its kernel
+ * (block_sparse_flash_attention_v2.py:113-144, 10-110); the lists come from the
+ * reference's index builders (:150-309) or the host-side mirrors of them.
+ *
+ * block_index is int32 [B, H, N/128, max_blocks] (device memory), each row ascending, exactly
+ * what the reference's builders hand to its kernel.  As there, query block m reads the first
+ * min(m + 1, max_blocks) entries of its row (:66), an index that occurs several times is
+ * attended several times (short rows are zero-padded and sorted, so key block 0 repeats), the
+ * row's own block gets a -inf causal mask (:76-77) and the softmax state starts empty (:52-54).
+ * Entries above the query block's own index are masked for every row there and are skipped
+ * here.  Logical shapes, strides and the GQA mapping are those of aa_params_t; N must be a
+ * multiple of 256 (the caller pads, as the reference's wrapper pads to 128, :334-339).
+ * The workspace holds the per-CTA tile lists (at most 2*max_blocks entries per pair of query
+ * blocks), their lengths and the status words.
+ */
+typedef struct aa_block_sparse {
+    int32_t B, H, Hkv, N, D;
+    int32_t dtype;                 /* AA_BF16                                              */
+    int32_t max_blocks;            /* last dimension of block_index (MAX_BLOCKS_PRE_ROW)   */
+    double  sm_scale;              /* 0 => D^-0.5 (block_sparse_flash_attention_v2.py:341) */
+    const void *q, *k, *v;
+    void       *out;
+    int64_t q_stride_b, q_stride_h, q_stride_n;
+    int64_t k_stride_b, k_stride_h, k_stride_n;
+    int64_t v_stride_b, v_stride_h, v_stride_n;
+    int64_t o_stride_b, o_stride_h, o_stride_n;
+    const int32_t *block_index;
+    void   *workspace;             /* 256-byte aligned, >= aa_block_sparse_workspace_bytes() */
+    size_t  workspace_bytes;
+} aa_block_sparse_t;
+
+int aa_block_sparse_workspace_bytes(const aa_block_sparse_t *a, size_t *bytes);
+/* Two launches on `stream`: the list merge and the attention kernel. */
+int aa_block_sparse_attend(const aa_block_sparse_t *a, void *stream);
+/* Synchronises the stream; AA_OK, AA_ERR_DEVICE_TIMEOUT (a bounded wait gave up) or
+ * AA_ERR_UNSORTED (a row of block_index was not ascending; the output is then undefined). */
+int aa_block_sparse_check_status(const aa_block_sparse_t *a, void *stream);
 
 const char *aa_strerror(int code);
 /* Text of the last CUDA error this library saw on the calling thread. */

@@ -140,6 +140,8 @@ def test_ctypes_mirrors_match_the_header(tmp_path):
         "aa_workspace_layout_t": (_lib.AALayout, ["m_off", "ids_off", "status_off", "total_bytes", "ids_per_head"]),
         "aa_stripes_static_args_t": (_lib.AAStripesStaticArgs, ["B", "theta", "q", "k_stride_n", "anchors", "ids"]),
         "aa_push_t": (_lib.AAPush, ["n_peers", "out"]),
+        "aa_block_sparse_t": (_lib.AABlockSparse, ["B", "max_blocks", "sm_scale", "q", "o_stride_n", "block_index",
+                                                   "workspace_bytes"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{os.path.abspath(HEADER)}"', "int main(void) {"]
     for cname, (_, fields) in checks.items():
