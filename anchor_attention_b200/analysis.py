@@ -10,6 +10,12 @@ selected.
 
     python -m anchor_attention_b200.analysis --shape qwen2.5-7b --seq 65536 --thetas 10,12,14
     python -m anchor_attention_b200.analysis --shape llama3.1-8b --seq 32768 --thetas 8,9,10,11,12 --q-shift 0.5
+    python -m anchor_attention_b200.analysis --shape llama3.1-8b --seq 32768 --block-thetas 0.05,0.1,0.2 --q-shift 0.5
+
+``--block-thetas`` adds the ablation the reference runs next to it: the block-granular
+comparator in its difference-aware mode (``block_sparse.py``; its sparsity ratio is the
+listed blocks over the causal blocks, block_sparse_flash_attention_v2.py:301-306) with the same
+recall measures.
 
 The dense comparator is torch's scaled_dot_product_attention (a library kernel;
 it is only the yardstick).  Inputs are the seeded synthetic tensors of
@@ -71,11 +77,32 @@ def theta_sweep(Q, K, V, thetas: Iterable[float], block_size: int = 128, step: i
     return rows
 
 
+def block_sparse_sweep(Q, K, V, thetas: Iterable[float], top_k: int = 1 << 30) -> List[Dict]:
+    """One row per theta of the block-granular comparator, difference-aware mode: its sparsity
+    ratio, recall at both thresholds and mean/max absolute difference to dense attention."""
+    from .block_sparse import block_sparse_attention
+    dense = dense_causal(Q, K, V)
+    rows = []
+    for th in thetas:
+        out, ratio = block_sparse_attention(Q, K, V, top_k, mode="top_difference_aware", theta=th,
+                                            return_sparsity_ratio=True)
+        diff = (out.float() - dense.float()).abs()
+        row = {"block_theta": th, "top_k": min(top_k, Q.shape[2] // 128), "sparsity_ratio": float(ratio),
+               "mean_abs_diff": float(diff.mean()), "max_abs_diff": float(diff.max())}
+        for t in RECALL_THRESHOLDS:
+            row[f"recall@{t}"] = float((diff < t).sum().item() / diff.numel())
+        rows.append(row)
+        del out, diff
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="qwen2.5-7b", choices=sorted(SHAPES))
     ap.add_argument("--seq", type=int, default=65536)
     ap.add_argument("--thetas", default="10,12,14")
+    ap.add_argument("--block-thetas", default="", help="also sweep the block-granular comparator over these thetas")
+    ap.add_argument("--block-top-k", type=int, default=1 << 30)
     ap.add_argument("--q-shift", type=float, default=0.0)
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
@@ -84,9 +111,13 @@ def main():
     from .synthetic import make_inputs
     H, Hkv = SHAPES[args.shape]
     Q, K, V = make_inputs(args.seq, H, Hkv, seed=args.seed, rope=True, q_shift=args.q_shift, device="cuda")
-    rows = theta_sweep(Q, K, V, [float(x) for x in args.thetas.split(",")])
-    print(json.dumps({"shape": args.shape, "heads": [H, Hkv], "seq": args.seq, "q_shift": args.q_shift,
-                      "data": "synthetic", "rows": rows}))
+    rows = theta_sweep(Q, K, V, [float(x) for x in args.thetas.split(",")]) if args.thetas else []
+    result = {"shape": args.shape, "heads": [H, Hkv], "seq": args.seq, "q_shift": args.q_shift,
+              "data": "synthetic", "rows": rows}
+    if args.block_thetas:
+        result["block_sparse_rows"] = block_sparse_sweep(Q, K, V, [float(x) for x in args.block_thetas.split(",")],
+                                                         args.block_top_k)
+    print(json.dumps(result))
 
 
 if __name__ == "__main__":

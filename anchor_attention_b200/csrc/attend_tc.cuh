@@ -13,7 +13,7 @@
 //            writes bf16(acc / l).  Reference: anchor_attn/src/ops/anchor_attn_v4.py:7-105.
 //   kBlock   (block-granular comparator)  whole 128-row key blocks from the merged block list
 //            of the CTA's two query tiles; an entry says which of the two tiles attends it (the
-//            other one hands the MMA warp a zero P); -inf causal mask on a tile's own block;
+//            other one gets no products for it); -inf causal mask on a tile's own block;
 //            state starts empty; writes bf16(acc / l).
 //            Reference: anchor_attn/src/ops/block_sparse_flash_attention_v2.py:10-110.
 //
@@ -250,25 +250,21 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         if ((tid & 31) == 0) mbar_arrive(bar);
     };
     uint32_t entry_next = (MODE == kBlock && ntiles > 0) ? (uint32_t)cx.list[0] : 0u;
+    int mine = 0;        // kBlock: tiles of this query tile so far (the MMA warp counts the same way)
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
         const uint32_t entry = entry_next;
-        if (MODE == kBlock && t + 1 < ntiles) entry_next = (uint32_t)cx.list[t + 1];
-        ok = mbar_wait(s_full_j, t & 1, abort_flag);
+        if (MODE == kBlock) {
+            if (t + 1 < ntiles) entry_next = (uint32_t)cx.list[t + 1];
+            // a block of the other query tile only: no S is produced for this one, nothing to do
+            if (!((entry >> (kBlockFlagShift + j)) & 1u)) continue;
+        }
+        const int seq = (MODE == kBlock) ? mine : t;      // which of this tile's score tiles
+        ++mine;
+        ok = mbar_wait(s_full_j, seq & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
-        if (MODE == kBlock && !((entry >> (kBlockFlagShift + j)) & 1u)) {
-            // the block belongs to the other query tile only: P = 0 leaves the accumulator as it is
-            uint32_t zero[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) zero[i] = 0u;
-            tmem_st32(tS, zero);
-            signal(p_part_j[0]);
-            tmem_st32(tS + 32, zero);
-            signal(p_part_j[1]);
-            continue;
-        }
         uint32_t sv[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
@@ -314,7 +310,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         // move the exponent reference only when some row of the warp needs it
         if (__any_sync(0xffffffffu, m_true > m_ref + kRescaleThreshold)) {
             const float alpha = fast_exp2(m_ref - m_true);
-            if (!(MODE != kStripe && t == 0)) {       // nothing accumulated yet when the state starts empty
+            if (!(MODE != kStripe && seq == 0)) {     // nothing accumulated yet when the state starts empty
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
                     uint32_t v[32];
@@ -617,29 +613,49 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             auto wait_all = [&](uint32_t bar, uint32_t parity) {
                 return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
             };
+            // kBlock: an entry of the tile list names the query tiles that attend the block; the
+            // other tile gets no Q K^T and no P V for it, and its barriers count its own tiles only.
+            // The list entries are read two tiles ahead.
+            uint32_t e_cur = 0xC0000000u, e_next = 0xC0000000u;
+            if (MODE == kBlock) {
+                e_cur = (uint32_t)idp[0];
+                e_next = ntiles > 1 ? (uint32_t)idp[1] : 0u;
+            }
+            auto attends = [&](uint32_t e, int j) { return MODE != kBlock || ((e >> (kBlockFlagShift + j)) & 1u) != 0u; };
+            int done[2] = {0, 0};          // P V products issued per query tile
             bool ok = wait_all(q_full(0), 0) && wait_all(q_full(1), 0) && wait_all(kv_full(0), 0);
             if (ok) {
                 fence_proxy_async();
                 tcgen05_fence_after();
-                issue_qk(0, slot_addr(0));
-                commit_if(issuer, s_full(0));
-                issue_qk(1, slot_addr(0));
-                commit_if(issuer, s_full(1));
+                if (attends(e_cur, 0)) {
+                    issue_qk(0, slot_addr(0));
+                    commit_if(issuer, s_full(0));
+                }
+                if (attends(e_cur, 1)) {
+                    issue_qk(1, slot_addr(0));
+                    commit_if(issuer, s_full(1));
+                }
                 commit_if(issuer, kv_empty(0));
             }
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int nv = 2 * t + 1, nk = 2 * t + 2;
+                uint32_t e_after = 0u;
+                if (MODE == kBlock && t + 2 < ntiles) e_after = (uint32_t)idp[t + 2];
                 ok = wait_all(kv_full(nv % kStages), (nv / kStages) & 1);
                 if (!ok) break;
                 fence_proxy_async();
                 for (int j = 0; j < 2 && ok; ++j) {
-                    for (int q = 0; q < kPParts && ok; ++q) {
-                        ok = wait_all(p_part(j, q), t & 1);
+                    if (attends(e_cur, j)) {
+                        const int seq = (MODE == kBlock) ? done[j] : t;
+                        for (int q = 0; q < kPParts && ok; ++q) {
+                            ok = wait_all(p_part(j, q), seq & 1);
+                            if (!ok) break;
+                            tcgen05_fence_after();
+                            issue_pv(j, slot_addr(nv), (seq > 0) || (MODE == kStripe) || q > 0, q * (8 / kPParts));
+                        }
                         if (!ok) break;
-                        tcgen05_fence_after();
-                        issue_pv(j, slot_addr(nv), (t > 0) || (MODE == kStripe) || q > 0, q * (8 / kPParts));
+                        ++done[j];
                     }
-                    if (!ok) break;
                     if (j == 1) commit_if(issuer, kv_empty(nv % kStages));
                     if (t + 1 < ntiles) {
                         if (j == 0) {
@@ -648,13 +664,17 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                             fence_proxy_async();
                             tcgen05_fence_after();
                         }
-                        issue_qk(j, slot_addr(nk));
-                        commit_if(issuer, s_full(j));
+                        if (attends(e_next, j)) {
+                            issue_qk(j, slot_addr(nk));
+                            commit_if(issuer, s_full(j));
+                        }
                         if (j == 1) commit_if(issuer, kv_empty(nk % kStages));
                     } else {
                         commit_if(issuer, o_done(j));
                     }
                 }
+                e_cur = e_next;
+                e_next = e_after;
             }
         } else if (warp >= 9 && ntiles > 0) {
             // =================================================== loaders (three warps)
