@@ -15,6 +15,11 @@ which every 128-row query block attends a list of whole 128-row key blocks
 
 K and V may carry fewer heads than Q (grouped-query attention).  Block sizes other than
 128 x 128 are not supported (no harness of the reference uses another).
+
+    python -m anchor_attention_b200.block_sparse --seq 32768 --mode top_k --top-k 64
+
+times the builder and the attention on seeded synthetic tensors (CUDA events) and prints one
+JSON line.
 """
 from __future__ import annotations
 
@@ -210,3 +215,59 @@ def block_sparse_attention(query, key, value, top_k: int, block_size_M: int = BL
         idx = torch.nn.functional.pad(idx, (0, 0, 0, 1))
     out = block_sparse_attend(query, key, value, idx, sm_scale)[..., :L, :]
     return (out, ratio) if return_sparsity_ratio else out
+
+
+def main():
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--seq", type=int, default=32768)
+    ap.add_argument("--heads", default="32,8")
+    ap.add_argument("--mode", default="top_k", choices=["top_k", "top_cdf", "top_difference_aware", "dense"])
+    ap.add_argument("--top-k", type=int, default=64)
+    ap.add_argument("--theta", type=float, default=0.5)
+    ap.add_argument("--cdf-threshold", type=float, default=0.95)
+    ap.add_argument("--q-shift", type=float, default=0.0)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device: the attention has no CPU path")
+    from .synthetic import make_inputs
+    H, Hkv = (int(x) for x in args.heads.split(","))
+    N = args.seq
+    Q, K, V = make_inputs(N, H, Hkv, seed=0, rope=True, q_shift=args.q_shift, device="cuda")
+    nb = N // BLOCK
+    sm = Q.shape[-1] ** -0.5
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record()
+    if args.mode == "dense":
+        idx = torch.arange(nb, dtype=torch.int32, device="cuda").expand(1, H, nb, nb).contiguous()
+        ratio = 1.0
+    elif args.mode == "top_k":
+        idx, ratio = build_block_index(Q, K, args.top_k)
+    elif args.mode == "top_cdf":
+        idx, ratio = build_block_index_top_cdf(Q, K, args.cdf_threshold, BLOCK, BLOCK, sm)
+    else:
+        idx, ratio = build_block_index_difference_aware(Q, K, BLOCK, BLOCK, args.theta, sm, args.top_k)
+    ev[1].record()
+    for _ in range(args.warmup):
+        block_sparse_attend(Q, K, V, idx, sm)
+    ev[2].record()
+    for _ in range(args.steps):
+        out = block_sparse_attend(Q, K, V, idx, sm)
+    ev[3].record()
+    block_sparse_attend(Q, K, V, idx, sm, out=out, check=True)
+    ms = ev[2].elapsed_time(ev[3]) / args.steps
+    # entries the kernel reads: min(m + 1, max_blocks) per query block (block_sparse_flash_attention_v2.py:66)
+    read = int(torch.minimum(torch.arange(1, nb + 1), torch.tensor(idx.shape[-1])).sum()) * H
+    print(json.dumps({"workload": f"block-sparse attention, seq {N}, {H}q/{Hkv}kv heads, mode {args.mode}",
+                      "max_blocks": int(idx.shape[-1]), "sparsity_ratio": float(ratio),
+                      "builder_ms": ev[0].elapsed_time(ev[1]), "attend_ms": ms, "entries_read": read,
+                      "tflops_on_entries_read": read * 4 * BLOCK ** 3 / ms / 1e9, "steps": args.steps,
+                      "data": "synthetic"}))
+
+
+if __name__ == "__main__":
+    main()
