@@ -2,7 +2,14 @@
 backed by hand-written sm_100a CUDA kernels behind a C ABI."""
 from .ops import (AnchorAttnCall, anchor_attn, anchor_attn_host, anchor_attn_without_anchor,
                   launches_per_forward)
-from .block_sparse import block_sparse_attention
+
+
+def __getattr__(name):
+    # the block-granular comparator is imported on first use
+    if name == "block_sparse_attention":
+        from .block_sparse import block_sparse_attention
+        return block_sparse_attention
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 __all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
            "launches_per_forward", "block_sparse_attention"]

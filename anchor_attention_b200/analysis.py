@@ -69,6 +69,7 @@ def theta_sweep(Q, K, V, thetas: Iterable[float], block_size: int = 128, step: i
                "density": float(call.counts.sum()) / cap if cap else 0.0,
                "sparsity_ratio": float(call.ratio()),
                "density_per_head_min": float(per_head.min()), "density_per_head_max": float(per_head.max()),
+               "density_per_head": [round(float(x), 4) for x in per_head.flatten()],
                "mean_abs_diff": float(diff.mean()), "max_abs_diff": float(diff.max())}
         for t in RECALL_THRESHOLDS:
             row[f"recall@{t}"] = float((diff < t).sum().item() / diff.numel())
