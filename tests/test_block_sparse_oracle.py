@@ -132,3 +132,28 @@ def test_dense_lists_give_causal_attention():
     out = block_sparse_attention_oracle(Q, K, V, idx, mode="fp32")
     dense = dense_causal_attention(Q, K, V)
     assert torch.allclose(out, dense, atol=2e-5)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_scatter_packing_equals_fill_and_sort(seed):
+    """The one-scatter packing of the shipped builders against the reference's recipe (zero rows,
+    selected indices in the first slots, sort; block_sparse_flash_attention_v2.py:228-239) on
+    random masks, empty rows included."""
+    from anchor_attention_b200.block_sparse import _pack
+    g = torch.Generator().manual_seed(seed)
+    B, H, nb = 2, 3, 11
+    valid = torch.rand(B, H, nb, nb, generator=g) < 0.3
+    valid[0, 0, 0] = False
+    valid[1, 2, 5] = True
+    width = int(valid.sum(-1).max())
+    want = torch.zeros(B, H, nb, width, dtype=torch.int64)
+    for b in range(B):
+        for h in range(H):
+            for m in range(nb):
+                sel = torch.arange(nb)[valid[b, h, m]]
+                want[b, h, m, :sel.numel()] = sel
+    want = want.sort(dim=-1).values.int()
+    assert torch.equal(_pack(valid, width), want)
+    # a wider row budget only adds leading zeros
+    wider = _pack(valid, width + 2)
+    assert torch.equal(wider[..., 2:], want) and (wider[..., :2] == 0).all()
