@@ -149,6 +149,50 @@ def cpu_sample(N, threads=None, limit_s=12.0):
     return ms, desc, cores
 
 
+def cpu_config0():
+    """The reference-runnable CPU case: one layer at seq 4096, 32 query / 8 KV heads, fp32, no
+    RoPE, whole operator through the CPU restatement without rounding (mode "fp32") on all host
+    threads; 1 warm-up + 3 timed calls, median.  With a GPU the bf16 CUDA operator runs on the
+    same inputs (cast to bf16) and its distance to the fp32 result is reported with its time.
+    Prints one JSON line of its own (not the benchmark line)."""
+    import torch
+    from oracle.anchor_oracle import anchor_attn_oracle, make_inputs
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    N0 = 4096
+    Q, K, V = make_inputs(N0, H, HKV, seed=0, rope=False, dtype=torch.float32)
+    times = []
+    res = None
+    for i in range(4):
+        t0 = time.perf_counter()
+        res = anchor_attn_oracle(Q, K, V, difference=THETA, mode="fp32")
+        if i > 0:
+            times.append((time.perf_counter() - t0) * 1e3)
+    G = BLOCK * STEP
+    cap = H * sum(b * G - 2 * BLOCK for b in range(1, N0 // G))
+    line = {"config": f"configs[0]: anchor_attn layer, seq {N0}, {H}q/{HKV}kv heads, head_dim {D}, fp32, no RoPE, "
+                      f"block {BLOCK}, step {STEP}, theta {THETA}",
+            "cpu_ms_median": statistics.median(times), "cpu_ms_runs": times, "cores": cores, "kind": "port",
+            "density": float(res.counts.sum()) / cap, "data": "synthetic"}
+    if torch.cuda.is_available():
+        from anchor_attention_b200 import AnchorAttnCall
+        call = AnchorAttnCall(Q.cuda().bfloat16(), K.cuda().bfloat16(), V.cuda().bfloat16(), None, BLOCK, STEP, THETA)
+        for _ in range(3):
+            call.run()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(10):
+            out = call.run()
+        ev1.record()
+        torch.cuda.synchronize()
+        call.check_status()
+        err = (out.float().cpu() - res.out).abs()
+        line.update({"gpu_bf16_ms": ev0.elapsed_time(ev1) / 10, "gpu_selected_columns": int(call.counts.sum()),
+                     "cpu_selected_columns": int(res.counts.sum()),
+                     "gpu_bf16_vs_cpu_fp32_max_abs": float(err.max()), "gpu_bf16_vs_cpu_fp32_mean_abs": float(err.mean())})
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -364,7 +408,13 @@ def main():
     ap.add_argument("--theta", type=float, default=THETA, help="auxiliary runs only; the benchmark uses 12")
     ap.add_argument("--exchange", default="push", choices=["push", "all_gather"],
                     help="how the head outputs reach every rank when N > 1")
+    ap.add_argument("--cpu-config0", action="store_true",
+                    help="auxiliary: time the CPU restatement on the fp32 4096-token case and stop")
     args = ap.parse_args()
+    if args.cpu_config0:
+        if int(os.environ.get("RANK", "0")) == 0:
+            cpu_config0()
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
