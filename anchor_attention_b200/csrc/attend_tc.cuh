@@ -536,6 +536,49 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
     }
 
+    if (MODE == kStripe && ntiles == 0) {
+        // Nothing selected for these rows (always so in the first big block): the output is step 1's
+        // state normalised, acc / l.  No tensor memory, no barriers: every warp streams whole rows
+        // (512 bytes in, 256 bytes out per row, coalesced), eight rows in flight per warp, with the
+        // arithmetic of the epilogue below.
+        constexpr int kWarps = kThreads / 32, kBatch = 8;
+        for (int row0 = warp; row0 < 2 * kTile; row0 += kWarps * kBatch) {
+            float l[kBatch];
+            float4 x[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int row = row0 + i * kWarps;
+                if (row < 2 * kTile) {
+                    const int64_t srow = (int64_t)hz * a.N + pair * 2 * kTile + row;
+                    l[i] = a.L[srow];
+                    x[i] = reinterpret_cast<const float4*>(a.Acc + srow * kD)[lane];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int row = row0 + i * kWarps;
+                if (row < 2 * kTile) {
+                    const float li = l[i], rl = __frcp_rn(li);
+                    auto div_l = [&](float v) {
+                        const float q0 = __fmul_rn(v, rl);
+                        const float rem = __fmaf_rn(-q0, li, v);
+                        return __fmaf_rn(rem, rl, q0);
+                    };
+                    uint2 o;
+                    o.x = pack_bf16x2(div_l(x[i].x), div_l(x[i].y));
+                    o.y = pack_bf16x2(div_l(x[i].z), div_l(x[i].w));
+                    const int64_t off = z * a.osb + h * a.osh + (int64_t)(pair * 2 * kTile + row) * a.osn + lane * 4;
+                    if (ta.n_peers == 0) {
+                        *reinterpret_cast<uint2*>(a.out + off) = o;
+                    } else {
+                        for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint2*>(ta.peers[pr] + off) = o;
+                    }
+                }
+            }
+        }
+        return;
+    }
+
     // ---- set-up ----
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
