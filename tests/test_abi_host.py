@@ -163,3 +163,42 @@ def test_ctypes_mirrors_match_the_header(tmp_path):
         seen += 1
     assert seen == sum(len(f) + 1 for _, f in checks.values())
     assert _lib.MAX_PEERS == 8 and _lib.STATIC_SCRATCH_BYTES == 8 << 20
+
+
+def _block_args(**kw):
+    a = _lib.AABlockSparse()
+    a.B, a.H, a.Hkv, a.N, a.D = 1, 4, 2, 1024, 128
+    a.dtype, a.max_blocks = _lib.AA_BF16, 5
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+def test_block_sparse_workspace_and_validation(lib):
+    """Host-only part of the comparator's entry points: workspace size and argument checks."""
+    need = ctypes.c_size_t(0)
+    a = _block_args()
+    assert lib.aa_block_sparse_workspace_bytes(ctypes.byref(a), ctypes.byref(need)) == 0
+    npairs, stride = 1024 // 256, 2 * 5
+    lists = 4 * npairs * stride * 4
+    assert need.value >= lists + 4 * npairs * 4 + 16 and need.value % 256 == 0
+    # max_blocks beyond the block count does not grow the lists further
+    big = ctypes.c_size_t(0)
+    assert lib.aa_block_sparse_workspace_bytes(ctypes.byref(_block_args(max_blocks=1000)), ctypes.byref(big)) == 0
+    assert big.value < 4 * npairs * 2 * 8 * 4 + 1024
+    for change, code in [(dict(D=64), -3), (dict(N=1024 + 128), -6), (dict(max_blocks=0), -2), (dict(Hkv=3), -2),
+                         (dict(dtype=1), -9)]:
+        assert lib.aa_block_sparse_workspace_bytes(ctypes.byref(_block_args(**change)), ctypes.byref(need)) == code
+    # NULL tensors and a missing workspace are refused before any CUDA call
+    assert lib.aa_block_sparse_attend(ctypes.byref(_block_args()), None) == -1
+    assert lib.aa_block_sparse_attend(None, None) == -1
+    assert b"ascending" in lib.aa_strerror(-13)
+
+
+def test_block_sparse_python_entry_refuses_cpu_tensors():
+    import torch
+    from anchor_attention_b200.block_sparse import block_sparse_attend
+    q = torch.zeros(1, 1, 256, 128, dtype=torch.bfloat16)
+    idx = torch.zeros(1, 1, 2, 1, dtype=torch.int32)
+    with pytest.raises(AssertionError, match="CUDA"):
+        block_sparse_attend(q, q, q, idx)
