@@ -18,7 +18,8 @@ EXPORTS = [
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
     "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
     "aa_selftest_wait_timeout", "aa_block_sparse_workspace_bytes", "aa_block_sparse_attend",
-    "aa_block_sparse_check_status",
+    "aa_block_sparse_check_status", "aa_validate_lists", "aa_step2_stripes_static_check_status",
+    "aa_peer_barrier",
 ]
 MAX_PEERS = 8
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -42,7 +43,8 @@ class AAParams(ctypes.Structure):
 class AALayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_size_t) for n in (
         "m_off", "l_off", "acc_off", "qpool_off", "apool_off", "bitmap_off", "counts_off",
-        "ids_off", "status_off", "total_bytes")] + [("ids_per_head", ctypes.c_int64)]
+        "ids_off", "status_off", "total_bytes")] + [("ids_per_head", ctypes.c_int64)] + [
+        (n, ctypes.c_size_t) for n in ("tile_slot_off", "gather_off", "gather_bytes", "min_bytes")]
 
 
 class AAStripesStaticArgs(ctypes.Structure):
@@ -78,6 +80,11 @@ class AAPush(ctypes.Structure):
     _fields_ = [("n_peers", ctypes.c_int32), ("out", ctypes.c_void_p * MAX_PEERS)]
 
 
+class AAPeerBarrier(ctypes.Structure):
+    _fields_ = [("n_peers", ctypes.c_int32), ("rank", ctypes.c_int32), ("epoch", ctypes.c_int32),
+                ("timeout_ms", ctypes.c_uint32), ("flags", ctypes.c_void_p * MAX_PEERS), ("status", ctypes.c_void_p)]
+
+
 _lib = None
 
 
@@ -97,13 +104,17 @@ def load():
     lib.aa_id_row_offset.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.aa_id_row_offset.restype = ctypes.c_int64
     for name in ("aa_forward", "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
-                 "aa_selftest_wait_timeout"):
+                 "aa_selftest_wait_timeout", "aa_validate_lists"):
         getattr(lib, name).argtypes = [P, ctypes.c_void_p]
         getattr(lib, name).restype = ctypes.c_int
     lib.aa_step2_stripes_static.argtypes = [ctypes.POINTER(AAStripesStaticArgs), ctypes.c_void_p]
     lib.aa_step2_stripes_static.restype = ctypes.c_int
+    lib.aa_step2_stripes_static_check_status.argtypes = [ctypes.c_void_p]
+    lib.aa_step2_stripes_static_check_status.restype = ctypes.c_int
     lib.aa_step3_sparse_push.argtypes = [P, ctypes.POINTER(AAPush), ctypes.c_void_p]
     lib.aa_step3_sparse_push.restype = ctypes.c_int
+    lib.aa_peer_barrier.argtypes = [ctypes.POINTER(AAPeerBarrier), ctypes.c_void_p]
+    lib.aa_peer_barrier.restype = ctypes.c_int
     PB = ctypes.POINTER(AABlockSparse)
     lib.aa_block_sparse_workspace_bytes.argtypes = [PB, ctypes.POINTER(ctypes.c_size_t)]
     lib.aa_block_sparse_workspace_bytes.restype = ctypes.c_int

@@ -12,6 +12,8 @@
 #include "attend_tc.cuh"
 #include "block_list.cuh"
 #include "common.cuh"
+#include "gather.cuh"
+#include "peer_barrier.cuh"
 #include "score_tc.cuh"
 #include "stripe.cuh"
 
@@ -51,9 +53,17 @@ int check_full(const aa_params_t* p, aa_workspace_layout_t* lay) {
     if (((uintptr_t)p->q | (uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)p->out) & 15) return AA_ERR_STRIDE;
     rc = aa_workspace_layout(p, lay);
     if (rc) return rc;
-    if (!p->workspace || ((uintptr_t)p->workspace & 255) || p->workspace_bytes < lay->total_bytes)
+    if (!p->workspace || ((uintptr_t)p->workspace & 255) || p->workspace_bytes < lay->min_bytes)
         return AA_ERR_WORKSPACE;
     return AA_OK;
+}
+
+// 64 KB gather slots the caller's workspace holds beyond the mandatory sections
+int gather_slots(const aa_params_t* p, const aa_workspace_layout_t& lay) {
+    const size_t have = (p->workspace_bytes - lay.gather_off) / (2 * (size_t)aa::tc::kTileBytes);
+    const size_t all = (size_t)p->B * p->H * (size_t)(lay.ids_per_head / aa::tc::kTile);
+    const size_t n = have < all ? have : all;
+    return (int)(n < (size_t)0x7FFFFFFF ? n : (size_t)0x7FFFFFFF);
 }
 
 aa::TensorView view(const void* ptr, int64_t sb, int64_t sh, int64_t sn) {
@@ -172,8 +182,6 @@ int make_gather_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, i
                     int* usable) {
     *usable = 0;
     memset(map, 0, sizeof(*map));
-    const char* mode = getenv("AA_GATHER");            // "cp_async" forces the per-thread gather (for A/B timing)
-    if (mode && strcmp(mode, "cp_async") == 0) return AA_OK;
     if (sn < 128 || sb < 0 || sh < 0) return AA_OK;
     int64_t max_row0 = 0;
     for (int z = 0; z < B; ++z)
@@ -214,6 +222,8 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     ta.a = attend_args(p, lay);
     ta.status = ws_ptr<int32_t>(p, lay.status_off);
     ta.n_peers = 0;
+    ta.tile_slot = nullptr;
+    ta.gather = nullptr;
     ta.list_stride = list_stride;
     for (int i = 0; i < aa::tc::kMaxPeers; ++i) ta.peers[i] = nullptr;
     if (push) {
@@ -230,6 +240,30 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     CUtensorMap kgmap, vgmap;
     ta.k_gather = ta.v_gather = 0;
     if (MODE == aa::kStripe) {
+        // first pass of step 3: the tiles that are not runs go to the gather scratch once
+        const int n_slots = gather_slots(p, lay);
+        const int NB = p->N / (p->block_size * p->step);
+        if (n_slots > 0 && NB > 1) {
+            int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
+            e = cudaMemsetAsync(counter, 0, sizeof(int32_t), st);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(gather slot counter)");
+            aa::GatherArgs ga;
+            ga.k = ta.a.k;
+            ga.v = ta.a.v;
+            ga.counts = ta.a.counts;
+            ga.ids = ta.a.ids;
+            ga.ids_per_head = lay.ids_per_head;
+            ga.tile_slot = ws_ptr<int32_t>(p, lay.tile_slot_off);
+            ga.scratch = ws_ptr<uint8_t>(p, lay.gather_off);
+            ga.slot_counter = counter;
+            ga.n_slots = n_slots;
+            ga.H = p->H; ga.Hkv = p->Hkv; ga.N = p->N; ga.step = p->step; ga.block = p->block_size;
+            aa::gather_tiles_kernel<<<dim3(aa::kGatherSplit, NB - 1, p->B * p->H), aa::kGatherThreads, 0, st>>>(ga);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return cuda_fail(e, "launch gather pass");
+            ta.tile_slot = ga.tile_slot;
+            ta.gather = ga.scratch;
+        }
         make_gather_map(&kgmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.k_gather);
         make_gather_map(&vgmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.v_gather);
     } else {
@@ -350,7 +384,13 @@ int aa_workspace_layout(const aa_params_t* p, aa_workspace_layout_t* lay) {
     lay->counts_off = off;  off = align_up(off + BH * NB * sizeof(int32_t));
     lay->ids_off = off;     off = align_up(off + BH * (size_t)lay->ids_per_head * sizeof(int32_t) + 256);
     lay->status_off = off;  off = align_up(off + 4 * sizeof(int32_t));
-    lay->total_bytes = off;
+    const size_t tiles = BH * (size_t)(lay->ids_per_head / aa::tc::kTile);
+    lay->tile_slot_off = off;  off = align_up(off + tiles * sizeof(int32_t) + 256);
+    lay->gather_off = off;
+    lay->min_bytes = off;
+    const size_t all = tiles * 2 * (size_t)aa::tc::kTileBytes;
+    lay->gather_bytes = all < AA_GATHER_SCRATCH_CAP ? all : AA_GATHER_SCRATCH_CAP;
+    lay->total_bytes = off + lay->gather_bytes;
     return AA_OK;
 }
 
@@ -416,7 +456,7 @@ int aa_step3_sparse(const aa_params_t* p, void* stream) {
 }
 
 int aa_step3_sparse_push(const aa_params_t* p, const aa_push_t* push, void* stream) {
-    if (!push) return AA_ERR_NULL;
+    if (!p || !push) return AA_ERR_NULL;
     if (push->n_peers < 1 || push->n_peers > AA_MAX_PEERS) return AA_ERR_SHAPE;
     for (int i = 0; i < push->n_peers; ++i) {
         if (!push->out[i]) return AA_ERR_NULL;
@@ -428,6 +468,26 @@ int aa_step3_sparse_push(const aa_params_t* p, const aa_push_t* push, void* stre
     int rc = check_full(&q, &lay);
     if (rc) return rc;
     return launch_attend_tc<aa::kStripe>(&q, lay, static_cast<cudaStream_t>(stream), push);
+}
+
+int aa_peer_barrier(const aa_peer_barrier_t* b, void* stream) {
+    if (!b || !b->status) return AA_ERR_NULL;
+    if (b->n_peers < 1 || b->n_peers > AA_MAX_PEERS || b->rank < 0 || b->rank >= b->n_peers) return AA_ERR_SHAPE;
+    aa::PeerBarrierArgs a;
+    for (int i = 0; i < aa::kBarrierMaxPeers; ++i) a.flags[i] = nullptr;
+    for (int i = 0; i < b->n_peers; ++i) {
+        if (!b->flags[i]) return AA_ERR_NULL;
+        if ((uintptr_t)b->flags[i] & 3) return AA_ERR_STRIDE;
+        a.flags[i] = static_cast<int32_t*>(b->flags[i]);
+    }
+    a.n_peers = b->n_peers;
+    a.rank = b->rank;
+    a.epoch = b->epoch;
+    a.timeout_ns = (unsigned long long)(b->timeout_ms ? b->timeout_ms : 10000u) * 1000000ull;
+    a.status = b->status;
+    aa::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AA_OK : cuda_fail(e, "launch peer barrier");
 }
 
 int aa_forward(const aa_params_t* p, void* stream) {
@@ -449,7 +509,24 @@ int aa_check_status(const aa_params_t* p, void* stream) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status)");
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
-    return status[0] == 0 ? AA_OK : AA_ERR_DEVICE_TIMEOUT;
+    if (status[0] != 0) return AA_ERR_DEVICE_TIMEOUT;
+    return status[1] == 0 ? AA_OK : AA_ERR_BAD_LIST;
+}
+
+int aa_validate_lists(const aa_params_t* p, void* stream) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t* flag = ws_ptr<int32_t>(p, lay.status_off) + 1;
+    cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(int32_t), st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(list flag)");
+    const int NB = p->N / (p->block_size * p->step);
+    aa::validate_lists_kernel<<<dim3(NB, p->B * p->H), 256, 0, st>>>(
+        ws_ptr<int32_t>(p, lay.counts_off), ws_ptr<int32_t>(p, lay.ids_off), lay.ids_per_head, p->N, p->step,
+        p->block_size, flag);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? AA_OK : cuda_fail(e, "launch list validation");
 }
 
 int aa_selftest_wait_timeout(const aa_params_t* p, void* stream) {
@@ -572,11 +649,12 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
                           a->N, a->block_size, s);
     if (rcp) return rcp;
     cudaError_t e = cudaSuccess;
+    // the status word of the bounded device-side waits lives at the end of the fixed array
+    // (aa_step2_stripes_static_check_status reads it back)
+    int32_t* status = reinterpret_cast<int32_t*>(sc + AA_STATIC_SCRATCH_BYTES - 256);
+    cudaError_t em = cudaMemsetAsync(status, 0, sizeof(int32_t), s);
+    if (em != cudaSuccess) return cuda_fail(em, "cudaMemsetAsync(static status)");
     if (NB > 1) {
-        // the status word of the bounded device-side waits lives at the end of the fixed array
-        int32_t* status = reinterpret_cast<int32_t*>(sc + AA_STATIC_SCRATCH_BYTES - 256);
-        cudaError_t em = cudaMemsetAsync(status, 0, sizeof(int32_t), s);
-        if (em != cudaSuccess) return cuda_fail(em, "cudaMemsetAsync(static status)");
         int rc2 = launch_score(a->k, a->k_stride_b, a->k_stride_h, a->k_stride_n, qpool, apool, bitmap, status, a->B,
                                a->H, a->Hkv, a->N, a->step, a->block_size, qk_scale, diff, s);
         if (rc2) return rc2;
@@ -586,6 +664,21 @@ int aa_step2_stripes_static(const aa_stripes_static_args_t* a, void* stream) {
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch compact (static)");
     return AA_OK;
+}
+
+int aa_step2_stripes_static_check_status(void* stream) {
+    void* base = nullptr;
+    int dev = 0;
+    int rc = static_scratch_for_current_device(&base, &dev);
+    if (rc) return rc;
+    int32_t status = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&status, static_cast<unsigned char*>(base) + AA_STATIC_SCRATCH_BYTES - 256,
+                                    sizeof(status), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(static status)");
+    e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return status == 0 ? AA_OK : AA_ERR_DEVICE_TIMEOUT;
 }
 
 }  // extern "C"
@@ -725,12 +818,13 @@ const char* aa_strerror(int code) {
         case AA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
         case AA_ERR_TOO_LARGE: return "problem too large for this entry point";
         case AA_ERR_UNSORTED: return "a block list is not in ascending order";
+        case AA_ERR_BAD_LIST: return "an id list in the workspace is malformed (count or id out of range, or not ascending)";
         default: return "unknown error";
     }
 }
 
 const char* aa_last_cuda_error(void) { return g_cuda_err; }
-int aa_version(void) { return 1; }
-int aa_launches_per_forward(void) { return 5; }
+int aa_version(void) { return 2; }
+int aa_launches_per_forward(void) { return 6; }
 
 }  // extern "C"

@@ -45,22 +45,14 @@
 namespace aa {
 namespace tc {
 
-#ifndef AA_LOADER_WARPS
-#define AA_LOADER_WARPS 3
-#endif
-constexpr int kLoaderWarps = AA_LOADER_WARPS;          // warps 9 .. 9 + kLoaderWarps - 1
+constexpr int kLoaderWarps = 3;                        // warps 9 .. 11
 constexpr int kThreads = (9 + kLoaderWarps) * 32;
-#ifndef AA_SOFTMAX_REGS
-#define AA_SOFTMAX_REGS 208
-#endif
-#ifndef AA_OTHER_REGS
-#define AA_OTHER_REGS (AA_LOADER_WARPS > 3 ? 48 : 88)
-#endif
+constexpr int kSoftmaxRegs = 208;                      // registers per thread after setmaxnreg: softmax warps
+constexpr int kOtherRegs = 88;                         //                                        MMA and loader warps
 // setmaxnreg only moves registers between the warps of the CTA: what the CTA gets at launch
 // (64 K registers / threads, rounded down to a multiple of 8, per thread) must cover the
 // re-allocated sizes, or the growing warps wait for ever.  Warps re-allocate in groups of four.
-static_assert(kLoaderWarps == 3 || kLoaderWarps == 7, "loader warps must fill whole groups of four warps");
-static_assert(kThreads * (65536 / kThreads / 8 * 8) >= 256 * AA_SOFTMAX_REGS + (kThreads - 256) * AA_OTHER_REGS,
+static_assert(kThreads * (65536 / kThreads / 8 * 8) >= 256 * kSoftmaxRegs + (kThreads - 256) * kOtherRegs,
               "register re-allocation exceeds the CTA's registers");
 constexpr int kStages = 5;
 constexpr int kTile = 128;                        // rows per query tile and per key tile
@@ -81,48 +73,15 @@ struct TcArgs {
     int vpos_n, vpos_h, vpos_b;
     int k_gather, v_gather;          // 1: the 2-D row-gather tensor map of K / V is usable
     int list_stride;                 // kBlock only: entries reserved per query-tile pair in a.ids
+    const int32_t* tile_slot;        // step 3 only: gather slot of every id tile ([B*H, ids_per_head/128]) or NULL
+    const uint8_t* gather;           // step 3 only: the 64 KB slots (K image, V image) the gather pass filled
     int n_peers;                     // step 3 only: > 0 -> write the output to peers[0 .. n_peers) instead of a.out
     __nv_bfloat16* peers[kMaxPeers]; // same element offsets and strides as a.out; may be other GPUs' memory
     int32_t* status;
 };
 
-// Tuning knobs (compile-time; the defaults are the measured best on B200: with the two
-// query tiles alternating on one tensor pipe the softmax is bound by instruction issue
-// as much as by the MUFU unit, so moving exponentials to the FMA pipe did not pay).
-#ifndef AA_POLY_SHARE
-#define AA_POLY_SHARE 0
-#endif
-#ifndef AA_ORDER_KV_MAJOR
-#define AA_ORDER_KV_MAJOR 1
-#endif
-#ifndef AA_TMA_ROWS
-#define AA_TMA_ROWS 32
-#endif
-constexpr int kTmaRows = AA_TMA_ROWS;       // rows of a gathered tile fetched by TMA row gathers (multiple of 4)
-constexpr int kPolyShare = AA_POLY_SHARE;   // element pairs out of every 4 whose exp2 is a polynomial (0..4)
+constexpr int kTmaRows = 32;                // rows of a gathered tile fetched by TMA row gathers (multiple of 4)
 constexpr int kPParts = 2;                  // P is handed to the MMA warp in two halves
-
-// 2^x for a pair of fp32 values on the FMA pipe: x = n + f with n = floor(x);
-// 2^f from a cubic (max relative error 8.6e-5, far below the bf16 rounding of P),
-// 2^n by adding n to the exponent field.  Inputs below -126 are clamped.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-    const float kMagic = 12582912.0f;   // 1.5 * 2^23: adding it leaves floor(x) in the low mantissa bits
-    x.x = fmaxf(x.x, -126.0f);
-    x.y = fmaxf(x.y, -126.0f);
-    unsigned long long xi = *reinterpret_cast<unsigned long long*>(&x), fli;
-    const float2 magic2 = make_float2(kMagic, kMagic);
-    asm("add.rm.f32x2 %0, %1, %2;" : "=l"(fli) : "l"(xi), "l"(*reinterpret_cast<const unsigned long long*>(&magic2)));
-    const float2 fl = *reinterpret_cast<float2*>(&fli);
-    const float2 n = __fadd2_rn(fl, make_float2(-kMagic, -kMagic));
-    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-    float2 p = __ffma2_rn(make_float2(0.07706617563962936f, 0.07706617563962936f), f,
-                          make_float2(0.22764593362808228f, 0.22764593362808228f));
-    p = __ffma2_rn(p, f, make_float2(0.6951165795326233f, 0.6951165795326233f));
-    p = __ffma2_rn(p, f, make_float2(1.f, 1.f));
-    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(fl.x) << 23));
-    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(fl.y) << 23));
-    return p;
-}
 
 // byte offset of (row, 16-byte chunk) inside a 32 KB tile made of two 128B-swizzled slabs
 __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
@@ -336,9 +295,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 const int e = c * 64 + 2 * i;
                 const float2 d = __fadd2_rn(make_float2(__uint_as_float(sv[e >> 5][e & 31]),
                                                         __uint_as_float(sv[(e + 1) >> 5][(e + 1) & 31])), neg_ref);
-                // kPolyShare of every 4 element pairs take the polynomial on the FMA pipe,
-                // the others the MUFU unit
-                const float2 p = ((i & 3) < kPolyShare) ? exp2_poly2(d) : make_float2(fast_exp2(d.x), fast_exp2(d.y));
+                const float2 p = make_float2(fast_exp2(d.x), fast_exp2(d.y));
                 rs[i & 3] = __fadd2_rn(rs[i & 3], p);
                 pk[i] = pack_bf16x2(p.x, p.y);
             }
@@ -494,9 +451,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kSmemQ + kSmemRing + 196);
 
     // ---- which work item ----
-    const int BH = a.B * a.H;
     const int npairs = a.N / (2 * kTile);
-#if AA_ORDER_KV_MAJOR
     // CTAs that run at the same time share one KV head: its K and V (2 x 256 B x N) stay in
     // L2 while the query heads of the group and their query-tile pairs (heaviest first) walk them
     const int Hg = a.H / a.Hkv;
@@ -506,19 +461,13 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     const int z = kvz / a.Hkv, kvh = kvz % a.Hkv;
     const int h = kvh * Hg + rem % Hg;
     const int hz = z * a.H + h;
-    (void)BH;
-#else
-    const int pair = npairs - 1 - (int)(blockIdx.x / BH);      // heaviest first
-    const int hz = blockIdx.x % BH;
-    const int z = hz / a.H, h = hz % a.H;
-    const int kvh = h / (a.H / a.Hkv);
-#endif
     const int G = a.block * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;
 
     int ntiles, n_init = 0, local_start = 0, count = 0;
     const int32_t* idp = nullptr;
+    const int32_t* slotp = nullptr;      // step 3: gather slots of this list's tiles
     if (MODE == kWindow) {
         const int end = (2 * pair + 2) * kTile;
         const int init_end = min(G, end);
@@ -530,10 +479,12 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         ntiles = count;
         idp = a.ids + (int64_t)hz * a.ids_per_head + (int64_t)pair * ta.list_stride;
     } else {
-        count = a.counts[(int64_t)hz * NB + b];
+        // never beyond the capacity of the big block's list, whatever the workspace holds
+        count = min(max(a.counts[(int64_t)hz * NB + b], 0), max(b * G - 2 * a.block, 0));
         ntiles = (count + kTile - 1) / kTile;
         const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)a.block * (b - 1));
         idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
+        if (ta.tile_slot) slotp = ta.tile_slot + (int64_t)hz * (a.ids_per_head / kTile) + row_off / kTile;
     }
 
     if (MODE == kStripe && ntiles == 0) {
@@ -605,7 +556,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
 
     if (warp < 8) {
         // =================================================== softmax warps
-        setmaxnreg_inc<AA_SOFTMAX_REGS>();
+        setmaxnreg_inc<kSoftmaxRegs>();
         SoftmaxCtx sc;
         sc.smem = smem;
         sc.tmem_base = tmem_base;
@@ -621,7 +572,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         sc.list = idp;
         softmax_role<MODE>(ta, sc, tid);
     } else {
-        setmaxnreg_dec<AA_OTHER_REGS>();
+        setmaxnreg_dec<kOtherRegs>();
         if (warp == 8 && ntiles > 0) {
             const bool issuer = elect_one();
             // =================================================== MMA issuer
@@ -730,34 +681,44 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             const int k_row0 = (int)(koff / a.k.sn), k_col0 = (int)(koff % a.k.sn);
             const int v_row0 = (int)(voff / a.v.sn), v_col0 = (int)(voff % a.v.sn);
             bool ok = true;
+            int row0 = 0, gslot = -1;
+            bool run = true;         // 128 consecutive rows -> one TMA tile
             for (int n = 0; n < 2 * ntiles && ok; ++n) {
                 const int slot = n % kStages, it = n / kStages;
+                const int t = n >> 1;
+                const bool is_v = n & 1;
+                // where the tile comes from is decided once, for its K half (before the wait for a
+                // free slot, so that the loads of the list entries overlap it)
+                if (!is_v) {
+                    if (MODE == kWindow) {
+                        row0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
+                    } else if (MODE == kBlock) {
+                        row0 = (int)((uint32_t)idp[t] & kBlockIdMask) * kTile;
+                    } else {
+                        const int s0 = t * kTile;
+                        run = false;
+                        gslot = slotp ? slotp[t] : -1;     // only meaningful when the tile is not a run
+                        if (s0 + kTile <= count) {
+                            row0 = idp[s0];
+                            run = (idp[s0 + kTile - 1] - row0) == kTile - 1;
+                        }
+                    }
+                }
                 if (it > 0) {
                     ok = mbar_wait(kv_empty(slot), (it - 1) & 1, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                 }
-                const int t = n >> 1;
-                const bool is_v = n & 1;
                 const uint32_t dst = ring_u + (uint32_t)slot * kTileBytes;
-                int row0 = 0;
-                bool run = true;     // 128 consecutive rows -> one TMA tile
-                if (MODE == kWindow) {
-                    row0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
-                } else if (MODE == kBlock) {
-                    row0 = (int)((uint32_t)idp[t] & kBlockIdMask) * kTile;
-                } else {
-                    const int s0 = t * kTile;
-                    run = false;
-                    if (s0 + kTile <= count) {
-                        row0 = idp[s0];
-                        run = (idp[s0 + kTile - 1] - row0) == kTile - 1;
-                    }
-                }
-                if (run) {
+                if (run || gslot >= 0) {
+                    // a run of 128 rows of K / V itself (two box loads), or the tile's image in the
+                    // gather scratch (one bulk copy)
                     if (lw == 0 && lane == 0) {
                         mbar_arrive_expect_tx(kv_full(slot), kTileBytes);
-                        if (is_v)
+                        if (!run)
+                            bulk_load(dst, ta.gather + (int64_t)gslot * (2 * kTileBytes) + (is_v ? kTileBytes : 0),
+                                      kTileBytes, kv_full(slot));
+                        else if (is_v)
                             tma_tile(dst, &vmap, kv_full(slot), ta.vpos_n, ta.vpos_h, ta.vpos_b, row0, kvh, z);
                         else
                             tma_tile(dst, &kmap, kv_full(slot), ta.kpos_n, ta.kpos_h, ta.kpos_b, row0, kvh, z);
@@ -801,6 +762,11 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                             if (s0 + 1 < count) id4.y = idp[s0 + 1];
                             if (s0 + 2 < count) id4.z = idp[s0 + 2];
                         }
+                        // ids are addresses from here on: keep them inside the tensor
+                        id4.x = min(max(id4.x, 0), a.N - 1);
+                        id4.y = min(max(id4.y, 0), a.N - 1);
+                        id4.z = min(max(id4.z, 0), a.N - 1);
+                        id4.w = min(max(id4.w, 0), a.N - 1);
                         const CUtensorMap* gm = is_v ? &vgmap : &kgmap;
                         const int r0 = is_v ? v_row0 : k_row0, c0 = is_v ? v_col0 : k_col0;
                         const uint32_t d = dst + (uint32_t)lane * 512u;
@@ -824,7 +790,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                         const int v1 = __shfl_sync(0xffffffffu, id_hi, rel & 31);
                         const int row = rel < 32 ? v0 : v1;
                         const bool valid = row >= 0;
-                        cp_async16(dst + sw_off(ra + rel, ch), base + (int64_t)(valid ? row : 0) * sn + ch * 8,
+                        cp_async16(dst + sw_off(ra + rel, ch), base + (int64_t)(valid ? min(row, a.N - 1) : 0) * sn + ch * 8,
                                    valid ? 16 : 0);
                     }
                     cp_async_mbar_arrive_noinc(kv_full(slot));

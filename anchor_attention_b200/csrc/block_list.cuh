@@ -38,6 +38,9 @@ merge_block_lists_kernel(const int32_t* __restrict__ block_index, int BH, int nu
     int i = 0, j = 0, n = 0;
     int prev0 = -1, prev1 = -1;
     bool sorted = true;
+    // the whole of both rows must ascend, also behind the entry at which the merge stops reading
+    for (int k = 1; k < n0; ++k) sorted = sorted && l0[k] >= l0[k - 1];
+    for (int k = 1; k < n1; ++k) sorted = sorted && l1[k] >= l1[k - 1];
     // a value above the tile's own block ends that tile's list (ascending order)
     int a = (i < n0) ? l0[i] : INT_MAX, b = (j < n1) ? l1[j] : INT_MAX;
     while (true) {

@@ -108,8 +108,12 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
         : "memory");
 }
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+// Untiled bulk copy global -> shared memory of this CTA: both addresses 16-byte aligned, the
+// size a multiple of 16 bytes; completion is signalled on `bar` as transferred bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 
 // ---------------------------------------------------------------- tensor memory
@@ -148,34 +152,10 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-// 32 lanes x 16 consecutive 32-bit columns
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
-__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- MMA
-// Shared-memory matrix descriptor for 128-byte-swizzled bf16 tiles whose 8-row
-// groups are 1024 bytes apart.  `lbo_bytes` is the distance between 64-element
-// groups along the contiguous dimension (only used by MN-major operands).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);            // start address
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
-    d |= (uint64_t)((1024u >> 4) & 0x3FFFu) << 32;      // stride byte offset: 8 rows of 128 B
-    d |= 1ull << 46;                                    // descriptor version (Blackwell)
-    d |= 2ull << 61;                                    // SWIZZLE_128B
-    return d;
-}
-
 // Instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 128, A K-major;
 // B K-major (b_mn_major = 0) or MN-major (1).
 __host__ __device__ constexpr uint32_t idesc_bf16_128x128(int b_mn_major) {

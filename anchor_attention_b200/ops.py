@@ -52,7 +52,12 @@ class AnchorAttnCall:
     look at the intermediate state)."""
 
     def __init__(self, Q, K, V, sm_scale=None, block_size=128, step=16, difference=12.0,
-                 out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None):
+                 out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                 gather_scratch_bytes: Optional[int] = None):
+        """``gather_scratch_bytes``: size of the scratch step 3 copies the selected K/V rows of
+        non-contiguous id tiles into (64 KB per tile).  None = the library's recommendation
+        (every tile, at most 8 GiB); 0 = none, every CTA gathers its rows itself.  Ignored when
+        ``workspace`` is given (its size decides)."""
         lib = _lib.load()
         assert Q.dim() == 4 and K.dim() == 4 and V.dim() == 4, "Q, K, V must be [B, H, N, D]"
         assert Q.is_cuda and K.is_cuda and V.is_cuda, "Q, K, V must be CUDA tensors (there is no CPU path)"
@@ -91,7 +96,8 @@ class AnchorAttnCall:
         self.layout = lay
         self.stream = torch.cuda.current_stream(Q.device)
         if workspace is None:
-            workspace = _workspace(Q.device, self.stream.cuda_stream, lay.total_bytes)
+            nbytes = lay.total_bytes if gather_scratch_bytes is None else lay.min_bytes + int(gather_scratch_bytes)
+            workspace = _workspace(Q.device, self.stream.cuda_stream, nbytes)
         self.workspace = workspace
         p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel()
         self.params = p
@@ -147,6 +153,17 @@ class AnchorAttnCall:
 
     def check_status(self):
         self._call(self._lib.aa_check_status)
+
+    def validate_lists(self):
+        """Enqueue the read-only check of the id lists in the workspace (counts within capacity,
+        ids ascending and inside the candidate range); ``check_status()`` then raises if a list is
+        malformed.  For callers that fill or keep the lists themselves before ``step3()``."""
+        self._call(self._lib.aa_validate_lists)
+
+    @property
+    def gather_slots_used(self) -> int:
+        """64 KB gather slots step 3 handed out in its last run (synchronises)."""
+        return int(self._view(self.layout.status_off, 4, torch.int32)[2])
 
     # ---- typed views of the workspace ----------------------------------
     def _view(self, off, count, dtype):

@@ -75,14 +75,26 @@ def patch_model_config(model, pattern: str, cfg=None):
     return cfg
 
 
+DENSE_CHUNK = 4096   # queries per call of the dense path: bounds the boolean mask to 4096 x kv_len
+
+
 def _dense_causal(query, key, value, scaling, q_offset):
     """Dense causal attention of ``query`` (positions q_offset .. q_offset+q-1) over
     all keys; the comparator path for the tail and for decode (the reference calls
-    flash-attn here, anchor_attention.py:76-88,101-113).  Returns [B,H,q,D]."""
+    flash-attn here, anchor_attention.py:76-88,101-113).  Returns [B,H,q,D].
+    A library call (torch SDPA), in chunks of DENSE_CHUNK queries so that the mask of a
+    chunked prefill (many queries against a long cache) stays small; a query chunk only
+    sees the keys up to its own last position."""
     q_len, kv_len = query.shape[2], key.shape[2]
-    pos_q = torch.arange(q_offset, q_offset + q_len, device=query.device)[:, None]
-    mask = torch.arange(kv_len, device=query.device)[None, :] <= pos_q
-    return F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling, enable_gqa=True)
+    outs = []
+    for c0 in range(0, q_len, DENSE_CHUNK):
+        c1 = min(q_len, c0 + DENSE_CHUNK)
+        hi = min(kv_len, q_offset + c1)                      # keys past the chunk's last query are masked anyway
+        pos_q = torch.arange(q_offset + c0, q_offset + c1, device=query.device)[:, None]
+        mask = torch.arange(hi, device=query.device)[None, :] <= pos_q
+        outs.append(F.scaled_dot_product_attention(query[:, :, c0:c1], key[:, :, :hi], value[:, :, :hi],
+                                                   attn_mask=mask, scale=scaling, enable_gqa=True))
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=2)
 
 
 _head_parallel_group = None
@@ -170,6 +182,12 @@ def patch_model(model, pattern: str, config=None):
     name = type(model).__name__.lower()
     if not any(t in name for t in ("llama", "qwen2", "qwen3", "mistral")):
         raise ValueError(f"Unsupported model type: {type(model).__name__}")
+    # the dense path (tail, decode) is plain causal attention: a model that restricts attention
+    # to a sliding window would silently get full attention there (the reference hands
+    # sliding_window to its dense call, modules/llama/anchor_attention.py:76-88)
+    window = getattr(model.config, "sliding_window", None)
+    if window is not None and getattr(model.config, "use_sliding_window", True):
+        raise ValueError(f"models with a sliding attention window (sliding_window={window}) are not supported")
     patch_model_config(model, pattern, config)
     AttentionInterface.register(ATTN_IMPLEMENTATION_NAME, anchor_attention_forward)
     model.config._attn_implementation = ATTN_IMPLEMENTATION_NAME

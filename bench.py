@@ -16,6 +16,19 @@ NVLink while it computes (default) or through one NCCL all-gather
 host cores on a bounded sample of the same workload and extrapolates to the
 layer (the reference's own kernels are Triton GPU kernels; its "PyTorch path"
 is not runnable).
+
+``--triton-bar --ref-root <checkout of the reference>`` is an optional leg of its
+own: it runs the reference's unmodified ``anchor_attn_test_time``
+(anchor_attn/src/ops/anchor_attn_v4.py:328-354, Triton kernels compiled on the
+spot) on the same inputs with CUDA events and prints one JSON line with its
+times next to this library's on the same GPU.  Nothing else in this file, and
+nothing in the package, imports the reference.
+
+Besides the timing the line carries ``parity`` (sampled (head, big block) pairs of
+the timed run's own output and id lists against the CPU oracle, outside the timed
+region), ``aux_sparse`` (step 3 on the labelled auxiliary distribution, where the
+id lists are sparse) and ``clock_normalised`` (step-3 cycles per key/value tile at
+two sequence lengths from the sampled SM clock).
 """
 import argparse
 import json
@@ -103,6 +116,19 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload_config(N, W, exchange, theta=THETA, note=""):
+    """The ``config`` object of the JSON line; both arms print the same one."""
+    if W > 1:
+        par = f"heads by KV group over {W} GPU(s), " + (
+            "step 3 stores its rows into every rank's output over NVLink, one barrier" if exchange == "push"
+            else "one NCCL all-gather")
+    else:
+        par = "single GPU"
+    return {"workload": f"anchor_attn layer, seq {N}, {H}q/{HKV}kv heads, head_dim {D}, block {BLOCK}, "
+                        f"step {STEP}, theta {theta}",
+            "parallelism": par, "exchange_note": note, "l2": "inputs_exceed_l2"}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -149,12 +175,12 @@ def cpu_sample(N, threads=None, limit_s=12.0):
     return ms, desc, cores
 
 
-def cpu_config0():
+def cpu_config0(with_gpu=True):
     """The reference-runnable CPU case: one layer at seq 4096, 32 query / 8 KV heads, fp32, no
     RoPE, whole operator through the CPU restatement without rounding (mode "fp32") on all host
-    threads; 1 warm-up + 3 timed calls, median.  With a GPU the bf16 CUDA operator runs on the
-    same inputs (cast to bf16) and its distance to the fp32 result is reported with its time.
-    Prints one JSON line of its own (not the benchmark line)."""
+    threads; 1 warm-up + 3 timed calls, median (measured, nothing extrapolated).  With a GPU
+    the bf16 CUDA operator runs on the same inputs (cast to bf16) and its distance to the fp32
+    result is reported with its time.  Returns the record."""
     import torch
     from oracle.anchor_oracle import anchor_attn_oracle, make_inputs
     cores = os.cpu_count()
@@ -174,7 +200,7 @@ def cpu_config0():
                       f"block {BLOCK}, step {STEP}, theta {THETA}",
             "cpu_ms_median": statistics.median(times), "cpu_ms_runs": times, "cores": cores, "kind": "port",
             "density": float(res.counts.sum()) / cap, "data": "synthetic"}
-    if torch.cuda.is_available():
+    if with_gpu and torch.cuda.is_available():
         from anchor_attention_b200 import AnchorAttnCall
         call = AnchorAttnCall(Q.cuda().bfloat16(), K.cuda().bfloat16(), V.cuda().bfloat16(), None, BLOCK, STEP, THETA)
         for _ in range(3):
@@ -190,7 +216,7 @@ def cpu_config0():
         line.update({"gpu_bf16_ms": ev0.elapsed_time(ev1) / 10, "gpu_selected_columns": int(call.counts.sum()),
                      "cpu_selected_columns": int(res.counts.sum()),
                      "gpu_bf16_vs_cpu_fp32_max_abs": float(err.max()), "gpu_bf16_vs_cpu_fp32_mean_abs": float(err.mean())})
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run_reference(args):
@@ -199,8 +225,10 @@ def run_reference(args):
         return
     vals = []
     desc, cores = "", 0
+    # every step is a bounded sample; the whole run stays within a few minutes
+    limit_s = max(2.0, min(12.0, 150.0 / (args.warmup + args.steps)))
     for i in range(args.warmup + args.steps):
-        ms, desc, cores = cpu_sample(args.seq)
+        ms, desc, cores = cpu_sample(args.seq, limit_s=limit_s)
         if i >= args.warmup:
             vals.append(ms)
     v = statistics.mean(vals)
@@ -208,8 +236,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": "ms", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": v, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"anchor_attn layer, seq {args.seq}, {H}q/{HKV}kv heads, head_dim {D}, "
-                               f"block {BLOCK}, step {STEP}, theta {THETA}"},
+        "config": workload_config(args.seq, args.gpus, args.exchange),
         "cpu_baseline": {"value": v, "unit": "ms", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -220,6 +247,158 @@ def run_reference(args):
 # --------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------
+def parity_check(call, Q, K, V, full, N, W, rank, q_lo, theta, dev):
+    """Outside the timed region: the run's own output and id lists against the CPU oracle on
+    sampled (head, big block) pairs -- heads {0, H-1} x big blocks {1, NB/2, NB-1}.  Head 0 is
+    checked by rank 0 and head H-1 by the last rank (which own them and hold their id lists);
+    the oracle's output rows are then broadcast and EVERY rank compares its copy of the
+    assembled output ``full`` [1,N,H,D] with them, so at N > 1 the rows a rank received from a
+    peer are checked as well.  Also compares a per-head checksum of all ranks' copies.
+    Returns the ``parity`` object of the JSON line (identical on every rank)."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle.anchor_oracle import oracle_big_blocks
+    from parity_util import OUT_MAX_ABS, OUT_MEAN_ABS, check_id_set
+    G = BLOCK * STEP
+    NB = N // G
+    blocks = sorted({min(1, NB - 1), NB // 2, NB - 1})
+    checkers = {0: 0, H - 1: W - 1}                      # head -> rank that runs the oracle for it
+    torch.set_num_threads(max(1, (os.cpu_count() or 2) // (2 if W > 1 else 1)))
+    rows = {}
+    sym_diff = selected = band = 0
+    ids_ok = True
+    t0 = time.perf_counter()
+    for head, owner in checkers.items():
+        if owner != rank:
+            continue
+        hl = head - q_lo
+        q, k, v = Q[0, hl].cpu(), K[0, hl // (H // HKV)].cpu(), V[0, hl // (H // HKV)].cpu()
+        ref = torch.empty((len(blocks), G, D), dtype=torch.float32)
+        counts = call.counts.cpu()
+        for i, b in enumerate(blocks):
+            M, L, Acc, oids, oout = oracle_big_blocks(q, k, v, [b], difference=theta)
+            ref[i] = oout[b * G:(b + 1) * G]
+            c = int(counts[0, hl, b])
+            off = call.id_row_offset(b)
+            ids = call.ids[0, hl, off:off + c].cpu()
+            selected += c
+            sym_diff += len(set(ids.tolist()) ^ set(oids[b].tolist()))
+            if b:
+                try:
+                    band += check_id_set(ids, q, k, torch.nan_to_num(M), D ** -0.5, theta, b, BLOCK, STEP)[0]
+                except AssertionError:
+                    ids_ok = False
+        rows[head] = ref.to(dev)
+    out_max = out_mean = 0.0
+    for head, owner in checkers.items():
+        ref = rows.get(head)
+        if ref is None:
+            ref = torch.empty((len(blocks), G, D), dtype=torch.float32, device=dev)
+        if W > 1:
+            dist.broadcast(ref, src=owner)
+        for i, b in enumerate(blocks):
+            err = (full[0, b * G:(b + 1) * G, head].float() - ref[i]).abs()
+            out_max = max(out_max, float(err.max()))
+            out_mean = max(out_mean, float(err.mean()))
+    # every rank's copy of the assembled output holds the same bits
+    sums = torch.stack([full[0, :, h].contiguous().view(torch.int16).to(torch.int64).sum() for h in range(H)])
+    stats = torch.tensor([out_max, out_mean, float(sym_diff), float(selected), float(band), 0.0 if ids_ok else 1.0],
+                         dtype=torch.float64, device=dev)
+    copies_equal = True
+    if W > 1:
+        hi, lo = sums.clone(), sums.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        copies_equal = bool(torch.equal(hi, lo))
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        stats = torch.stack([mx[0], mx[1], sm[2], sm[3], sm[4], mx[5]])
+    out_max, out_mean = stats[0].item(), stats[1].item()
+    ok = out_max <= OUT_MAX_ABS and out_mean <= OUT_MEAN_ABS and stats[5].item() == 0.0 and copies_equal
+    return {"pairs": [[h, b] for h in checkers for b in blocks], "rows_checked_on": f"all {W} rank(s)",
+            "selected": int(stats[3].item()), "sym_diff": int(stats[2].item()), "tie_band": int(stats[4].item()),
+            "ids_within_tie_band": stats[5].item() == 0.0, "out_max": out_max, "out_mean": out_mean,
+            "tolerance": {"out_max": OUT_MAX_ABS, "out_mean": OUT_MEAN_ABS}, "copies_equal": copies_equal,
+            "oracle_s": time.perf_counter() - t0, "ok": bool(ok)}
+
+
+def timed_step3(call, seconds, sampler_index):
+    """Repeats the whole operator for about ``seconds`` with the SM clock sampled, step 3 bracketed by
+    CUDA events.  Returns (mean step-3 ms, median SM MHz)."""
+    import torch
+    for _ in range(3):
+        call.run()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(sampler_index)
+    sampler.start()
+    evs = []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end:
+        for _ in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            call.step1()
+            call.step2()
+            a.record()
+            call.step3()
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    return statistics.mean(a.elapsed_time(b) for a, b in evs), clocks.get("sm_mhz")
+
+
+def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
+    """Single-GPU extras, outside the headline timing.
+    aux_sparse: the labelled AUXILIARY distribution (q_shift 0.5) at 32768 tokens, where the id
+    lists are sparse and step 3 runs through its gather pass: density, step-3 time (gather pass
+    included) and TFLOP/s on the selected pairs for theta 9 and 10.
+    clock_normalised: step-3 SM cycles per 128-id tile and query-tile pair (launch time x median
+    sampled SM clock / tile pairs / 148 SMs) for the benchmark launch and for the dense
+    32768-token layer, each from a loop of about two seconds; equal cycles mean the difference in
+    TFLOP/s between the two sizes is the clock under the power cap."""
+    import torch
+    from anchor_attention_b200 import AnchorAttnCall
+    from anchor_attention_b200.synthetic import make_inputs
+    N_AUX = 32768
+    G = BLOCK * STEP
+    cap = H * sum(b * G - 2 * BLOCK for b in range(1, N_AUX // G))
+    aux = {"note": "AUXILIARY distribution, not the benchmark configuration", "seq": N_AUX, "q_shift": 0.5, "cases": []}
+    Q, K, V = make_inputs(N_AUX, H, HKV, seed=0, rope=True, device=dev, q_shift=0.5)
+    for theta in (9.0, 10.0):
+        call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, theta)
+        for _ in range(3):
+            call.run()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(10)]
+        for e in ev:
+            e[0].record(); call.step1(); e[1].record(); call.step2(); e[2].record(); call.step3(); e[3].record()
+        torch.cuda.synchronize()
+        call.check_status()
+        t = [statistics.median(e[i].elapsed_time(e[i + 1]) for e in ev) for i in range(3)]
+        cnt = int(call.counts.sum())
+        aux["cases"].append({"theta": theta, "density": cnt / cap, "step1_ms": t[0], "step2_ms": t[1], "step3_ms": t[2],
+                             "gathered_tiles": call.gather_slots_used,
+                             "step3_tflops_selected_pairs": 4 * D * G * cnt / (t[2] * 1e-3) / 1e12})
+    del Q, K, V
+    Q, K, V = make_inputs(N_AUX, H, HKV, seed=0, rope=True, device=dev)
+    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA)
+    ms32, mhz32 = timed_step3(call, 2.0, local)
+    cnt32 = int(call.counts.sum())
+
+    def cycles(ms, mhz, cnt):
+        pairs = cnt / BLOCK * (G // (2 * BLOCK))          # (128-id tile, 256-row query pair) products
+        return ms * 1e-3 * mhz * 1e6 * 148 / pairs if mhz else None
+
+    norm = {"note": "step-3 SM cycles per (128-id tile x 256 query rows), from launch time x median sampled SM clock",
+            f"seq{N}": {"step3_ms": main_step3_ms, "sm_mhz": main_mhz, "cycles_per_tile_pair": cycles(main_step3_ms, main_mhz, main_counts),
+                        "tflops": 4 * D * G * main_counts / (main_step3_ms * 1e-3) / 1e12},
+            f"seq{N_AUX}": {"step3_ms": ms32, "sm_mhz": mhz32, "cycles_per_tile_pair": cycles(ms32, mhz32, cnt32),
+                            "tflops": 4 * D * G * cnt32 / (ms32 * 1e-3) / 1e12}}
+    return aux, norm
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -248,7 +427,7 @@ def run_ours(args):
     exchange_note = ""
     if push:
         # every rank's copy of the assembled [1,N,H,D] output lives in symmetric memory; step 3
-        # stores this rank's heads into all copies, a barrier replaces the all-gather
+        # stores this rank's heads into all copies, a flag barrier replaces the all-gather
         try:
             pushed = PushedOutput(1, N, H, D, torch.bfloat16, dev)
             failed = 0
@@ -269,6 +448,7 @@ def run_ours(args):
         out_view = out_local.permute(0, 2, 1, 3)
         gathered = torch.empty((W, 1, N, h, D), dtype=torch.bfloat16, device=dev) if W > 1 else None
     call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA, out=out_view)
+    last = {}
 
     def step(ev=None):
         call.step1()
@@ -276,16 +456,19 @@ def run_ours(args):
         if ev is not None:
             ev[0].record()
         if push:
-            _, ptrs, handle = pushed.next()
+            buf, ptrs = pushed.next()
             call.step3_push([p + head_off for p in ptrs])
         else:
             call.step3()
         if ev is not None:
             ev[1].record()
         if push:
-            handle.barrier(channel=0)
+            pushed.barrier()
+            last["full"] = buf
         elif W > 1:
-            gather_heads(out_local, None, gathered)
+            last["full"] = gather_heads(out_local, None, gathered)
+        else:
+            last["full"] = out_local
 
     def barrier():
         if W > 1:
@@ -310,6 +493,13 @@ def run_ours(args):
     ms = t0.elapsed_time(t1) / args.steps
     k3_ms = statistics.mean(a.elapsed_time(b) for a, b in k_ev)
     counts_total = int(call.counts.sum())
+    # no bounded device-side wait gave up during the timed loop (synchronises)
+    call.check_status()
+    if push:
+        pushed.check_status()
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(call, Q, K, V, last["full"], N, W, rank, q_lo, THETA, dev)
 
     # ---- end to end through the public entry point, host buffers in, host result out
     from anchor_attention_b200 import anchor_attn_host
@@ -324,10 +514,11 @@ def run_ours(args):
             # host buffers in, host buffer out; the KV-head groups are streamed so that the copies
             # of one group overlap the computation of another
             anchor_attn_host(hq, hk, hv, hout, None, BLOCK, STEP, THETA, device=dev)
-            return
-        dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-        full = sharded(dq, dk, dv)                                       # [1,N,H,D] on every rank
-        hout.copy_(full[:, :, q_lo:q_hi].permute(0, 2, 1, 3), non_blocking=True)
+        else:
+            # each rank streams its heads through the device (copies overlap the computation of
+            # the previous head); every rank ends with the assembled output on the device and
+            # its own heads' result back in host memory
+            sharded.host_call(hq, hk, hv, hout)
 
     e2e_step()
     barrier()
@@ -338,9 +529,12 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    # the end-to-end result equals the device-resident result bit for bit
+    e2e_equal = bool(torch.equal(hout.to(dev).permute(0, 2, 1, 3), last["full"][:, :, q_lo:q_hi]))
 
     # ---- max over ranks
-    stats = torch.tensor([ms, k3_ms, e2e_ms, float(counts_total)], dtype=torch.float64, device=dev)
+    stats = torch.tensor([ms, k3_ms, e2e_ms, float(counts_total), 0.0 if e2e_equal else 1.0], dtype=torch.float64,
+                         device=dev)
     if W > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
@@ -348,6 +542,7 @@ def run_ours(args):
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         ms, k3_ms, e2e_ms = mx[0].item(), mx[1].item(), mx[2].item()
         counts_all = int(sm[3].item())
+        e2e_equal = mx[4].item() == 0.0
     else:
         counts_all = counts_total
     if rank == 0:
@@ -367,14 +562,8 @@ def run_ours(args):
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16",
             "data": f"synthetic, AUXILIARY distribution (q_shift {args.q_shift}, theta {args.theta})" if aux else "synthetic",
-            "config": {"workload": f"anchor_attn layer, seq {N}, {H}q/{HKV}kv heads, head_dim {D}, block {BLOCK}, "
-                                   f"step {STEP}, theta {THETA}",
-                       "parallelism": (f"heads by KV group over {W} GPU(s), " +
-                                       ("step 3 stores its rows into every rank's output over NVLink, one barrier"
-                                        if push else "one NCCL all-gather")) if W > 1 else "single GPU",
-                       "exchange_note": exchange_note,
-                       "l2": "inputs_exceed_l2", "density": counts_all / cap if cap else 0.0,
-                       "selected_columns": counts_all},
+            "config": workload_config(N, W, args.exchange, THETA, exchange_note),
+            "selection": {"density": counts_all / cap if cap else 0.0, "selected_columns": counts_all},
             "algorithmic_tflop": {"step1": f1 / 1e12, "step2": f2 / 1e12, "step3": f3 / 1e12},
             "layer_tflops": (f1 + f2 + f3) / (ms * 1e-3) / 1e12,
             "roofline": {"kernel": "step 3 (gathered sparse flash attention)", "bound": "tensor",
@@ -382,16 +571,94 @@ def run_ours(args):
                          "traffic": traffic, "traffic_unit": f"DRAM bytes per launch (ncu capture at {ref_n} tokens, scaled by tile loads)",
                          "peak_source": f"{peak_src} (sustained bf16)", "launch_ms": k3_ms},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": W * sum(t.numel() * 2 for t in (hq, hk, hv)),
-                    "d2h_bytes_per_step": W * hout.numel() * 2, "steps": e2e_steps},
+                    "d2h_bytes_per_step": W * hout.numel() * 2, "steps": e2e_steps, "equals_device_result": e2e_equal},
             "gpu_launches": launches_per_forward() * args.steps,
+            "device_status": "ok",
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity"] = parity
+        if W == 1 and not args.no_aux:
+            del hq, hk, hv, hout
+            line["aux_sparse"], line["clock_normalised"] = aux_measurements(
+                dev, local, k3_ms, clocks.get("sm_mhz") if clocks else None, counts_all, N)
         if W == 1 and not args.no_cpu_baseline:
             v, desc, cores = cpu_sample(N)
             line["cpu_baseline"] = {"value": v, "unit": "ms", "cores": cores, "kind": "port", "sample": desc}
+            c0 = cpu_config0(with_gpu=False)
+            line["cpu_baseline"]["config0_ms"] = c0["cpu_ms_median"]
+            line["cpu_baseline"]["config0"] = (c0["config"] + f"; measured, not extrapolated: median of 3 calls on "
+                                               f"{c0['cores']} threads")
         print(json.dumps(line), flush=True)
     if W > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------
+# The reference's own kernels on this GPU (optional leg)
+# --------------------------------------------------------------------------
+def run_triton_bar(args):
+    """Times the reference's unmodified ``anchor_attn_test_time`` (anchor_attn/src/ops/
+    anchor_attn_v4.py:328-354: search = steps 1 + 2, compute = step 3; Triton kernels compiled
+    for this GPU) and this library on the same inputs: 3 warm-up calls, then CUDA events around
+    ``--steps`` calls, median.  K and V are expanded to the query head count for the reference,
+    as its caller does (modules/llama/anchor_attention.py:89-91).  Prints one JSON line."""
+    import importlib
+    import torch
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    line = {"leg": "triton_bar", "seq": args.seq, "heads": f"{H}q/{HKV}kv", "theta": THETA}
+    root = args.ref_root
+    if not root or not os.path.isdir(root):
+        line["triton_bar"] = f"unavailable: no reference checkout at {root!r} (pass --ref-root)"
+        print(json.dumps(line), flush=True)
+        return
+    try:
+        sys.path.insert(0, os.path.abspath(root))
+        ref = importlib.import_module("anchor_attn.src.ops.anchor_attn_v4")
+    except Exception as e:      # import of the reference (or of Triton) failed
+        line["triton_bar"] = f"unavailable: {type(e).__name__}: {e}"
+        print(json.dumps(line), flush=True)
+        return
+    from anchor_attention_b200 import AnchorAttnCall
+    from anchor_attention_b200.synthetic import make_inputs
+    dev = torch.device("cuda", 0)
+    N = args.seq
+    Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev)
+    Ke, Ve = (t.repeat_interleave(H // HKV, dim=1).contiguous() for t in (K, V))
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    full, search, compute = [], [], []
+    out_ref = None
+    for i in range(3 + args.steps):
+        a, b = ev(), ev()
+        a.record()
+        out_ref, ratio, s_ms, c_ms = ref.anchor_attn_test_time(Q, Ke, Ve, None, BLOCK, STEP, THETA, True)
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            full.append(a.elapsed_time(b)); search.append(s_ms); compute.append(c_ms)
+    del Ke, Ve
+    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA)
+    ours = []
+    for i in range(3 + args.steps):
+        a, b = ev(), ev()
+        a.record()
+        out = call.run()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ours.append(a.elapsed_time(b))
+    err = (out.float() - out_ref.float()).abs()
+    line["triton_bar"] = {"ms": statistics.median(full), "step12_ms": statistics.median(search),
+                          "step3_ms": statistics.median(compute), "sparsity_ratio": float(ratio),
+                          "timing": "ms: CUDA events around anchor_attn_test_time; step12/step3: its own wall clocks"}
+    line["ours_ms"] = statistics.median(ours)
+    line["speedup"] = statistics.median(full) / statistics.median(ours)
+    line["out_max_abs_diff"], line["out_mean_abs_diff"] = float(err.max()), float(err.mean())
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -410,10 +677,18 @@ def main():
                     help="how the head outputs reach every rank when N > 1")
     ap.add_argument("--cpu-config0", action="store_true",
                     help="auxiliary: time the CPU restatement on the fp32 4096-token case and stop")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the run's own output")
+    ap.add_argument("--no-aux", action="store_true", help="skip the auxiliary sparse-regime and clock-normalised runs")
+    ap.add_argument("--triton-bar", action="store_true",
+                    help="optional leg: time the reference's own Triton kernels from --ref-root on this GPU and stop")
+    ap.add_argument("--ref-root", default=None, help="checkout of the reference project (for --triton-bar only)")
     args = ap.parse_args()
+    if args.triton_bar:
+        run_triton_bar(args)
+        return
     if args.cpu_config0:
         if int(os.environ.get("RANK", "0")) == 0:
-            cpu_config0()
+            print(json.dumps(cpu_config0()), flush=True)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -37,7 +37,8 @@ enum {
     AA_ERR_CUDA = -10,         /* a CUDA runtime/driver call failed (see aa_last_cuda_error) */
     AA_ERR_DEVICE_TIMEOUT = -11,/* a bounded device-side wait gave up (status word)  */
     AA_ERR_TOO_LARGE = -12,    /* size beyond what an entry point supports           */
-    AA_ERR_UNSORTED = -13      /* a key-block list of the comparator is not ascending */
+    AA_ERR_UNSORTED = -13,     /* a key-block list of the comparator is not ascending */
+    AA_ERR_BAD_LIST = -14      /* aa_validate_lists found a count or an id out of range  */
 };
 
 enum { AA_BF16 = 0 };
@@ -70,7 +71,8 @@ typedef struct aa_params {
     int64_t k_stride_b, k_stride_h, k_stride_n;
     int64_t v_stride_b, v_stride_h, v_stride_n;
     int64_t o_stride_b, o_stride_h, o_stride_n;
-    void   *workspace;         /* device scratch, 256-byte aligned, >= aa_workspace_bytes() */
+    void   *workspace;         /* device scratch, 256-byte aligned; aa_workspace_bytes() is the
+                                  recommended size, aa_workspace_layout().min_bytes the least   */
     size_t  workspace_bytes;
 } aa_params_t;
 
@@ -90,10 +92,22 @@ typedef struct aa_workspace_layout {
     size_t bitmap_off;   /* uint32  [B,H,NB,N/32]    hit bitmap of step 2                       */
     size_t counts_off;   /* int32   [B,H,NB]         selected columns per big block             */
     size_t ids_off;      /* int32   [B,H,ids_per_head] ascending selected column ids            */
-    size_t status_off;   /* int32   [4]              device status word(s), 0 = ok              */
-    size_t total_bytes;
+    size_t status_off;   /* int32   [4]              [0] a bounded device-side wait gave up,
+                                                     [1] aa_validate_lists found a bad list,
+                                                     [2] gather slots handed out by step 3       */
+    size_t total_bytes;  /* recommended workspace size: min_bytes + gather_bytes                 */
     int64_t ids_per_head;
+    size_t tile_slot_off;/* int32   [B,H,ids_per_head/128] gather slot of every 128-id tile, or -1 */
+    size_t gather_off;   /* gather scratch of step 3: 64 KB slots (K image, V image) for the id
+                            tiles that are not runs of consecutive rows; the LAST section        */
+    size_t gather_bytes; /* recommended size of it: every tile of every list, but at most
+                            AA_GATHER_SCRATCH_CAP bytes                                          */
+    size_t min_bytes;    /* smallest workspace the entry points accept (= gather_off).  Step 3
+                            uses as many 64 KB slots as workspace_bytes - gather_off holds;
+                            tiles without a slot are gathered inside the attention kernel       */
 } aa_workspace_layout_t;
+
+#define AA_GATHER_SCRATCH_CAP ((size_t)8 << 30)
 
 /* Size and layout of the workspace for a problem (only the shape fields of p
  * are read).  Host-only, no CUDA calls. */
@@ -118,8 +132,23 @@ int aa_step2_stripes(const aa_params_t *p, void *stream);
 
 /* Step 3, gathered sparse flash attention merged with the step-1 state:
  * reads M, L, Acc, counts, ids; writes out.  Replaces the launch of
- * _triton_stripe_sparse_attn_fwd_kernel_step3 (anchor_attn_v4.py:246-268). */
+ * _triton_stripe_sparse_attn_fwd_kernel_step3 (anchor_attn_v4.py:246-268).
+ * Two kernels: a gather pass that copies the selected K/V rows of every id tile that is
+ * not a run of consecutive rows into the workspace's gather scratch once (the eight CTAs
+ * that serve the 2048 query rows of a big block then fetch it with bulk copies instead
+ * of gathering the same rows eight times), and the attention kernel.  Counts are clamped
+ * to the capacity of their big block and ids to [0, N) before they are used as
+ * addresses, so a stale or foreign workspace cannot make the kernels read outside K/V
+ * (aa_validate_lists tells whether the lists are well formed). */
 int aa_step3_sparse(const aa_params_t *p, void *stream);
+
+/* Checks the id lists in the workspace without gathering anything: every count within
+ * [0, b*G - 2*block_size], every list ascending and inside [block_size, b*G - block_size)
+ * (the shape get_mask_test.py:111-124 produces).  Enqueues one small kernel; a following
+ * aa_check_status returns AA_ERR_BAD_LIST if a list is malformed.  For callers that fill
+ * or keep the lists themselves before aa_step3_sparse.  (No counterpart in the
+ * reference, whose step 3 trusts its lists.) */
+int aa_validate_lists(const aa_params_t *p, void *stream);
 
 /* Step 3 for head-parallel runs: identical to aa_step3_sparse, except that every output
  * row is stored to push->out[0 .. n_peers) instead of p->out -- same element offsets and
@@ -135,8 +164,28 @@ typedef struct aa_push {
 } aa_push_t;
 int aa_step3_sparse_push(const aa_params_t *p, const aa_push_t *push, void *stream);
 
-/* Reads the device status word (synchronises the stream first).  Returns AA_OK
- * or AA_ERR_DEVICE_TIMEOUT / AA_ERR_CUDA. */
+/* Barrier between the ranks of a head-parallel layer, to follow aa_step3_sparse_push: the
+ * rank announces epoch `epoch` in every peer's flag array (flags[p] + rank) and waits until
+ * every peer has announced it in this rank's own array (flags[rank] + p).  Plain peer
+ * stores and loads, release / acquire at system scope.  flags[p] is rank p's array of at
+ * least n_peers int32 in device memory every rank can address (symmetric or IPC-opened),
+ * zero before the first use; `epoch` must grow by one with every call and be the same on
+ * all ranks.  The wait is bounded: after timeout_ms (0 = 10 s) without a peer's
+ * announcement the kernel sets *status (a device int32 of this rank, which the caller
+ * zeroes once) to 1 and returns, so a rank that left between steps cannot hang the
+ * others' GPUs; read *status on the host before using the assembled output.  One launch,
+ * no synchronisation.  (No counterpart in the reference, which is single-GPU.) */
+typedef struct aa_peer_barrier {
+    int32_t n_peers, rank;
+    int32_t epoch;
+    uint32_t timeout_ms;
+    void   *flags[AA_MAX_PEERS];
+    int32_t *status;
+} aa_peer_barrier_t;
+int aa_peer_barrier(const aa_peer_barrier_t *b, void *stream);
+
+/* Reads the device status words (synchronises the stream first).  Returns AA_OK,
+ * AA_ERR_DEVICE_TIMEOUT, AA_ERR_BAD_LIST or AA_ERR_CUDA. */
 int aa_check_status(const aa_params_t *p, void *stream);
 
 /* Self-test of the failure path: enqueues a one-warp kernel that waits on a barrier nothing
@@ -171,8 +220,8 @@ int aa_total_selected(const aa_params_t *p, void *stream, int64_t *total);
  *
  * - Problems whose intermediates exceed the array are refused with
  *   AA_ERR_TOO_LARGE; nothing is launched.  The need is
- *   B*H*(N/128)*(256+4) + B*H*NB*(N/32)*4 + 256 bytes plus alignment padding,
- *   e.g. 4.1 MiB for B*H = 32, N = 32768.
+ *   B*H*(N/block_size)*(256+4) + B*H*NB*(N/32)*4 + 256 bytes plus alignment padding
+ *   (NB = N / (block_size*step)), e.g. 4.1 MiB for B*H = 32, N = 32768, block_size 128.
  * - It calls no cudaMalloc / cudaFree and no allocating library routine.
  * - The first call on a device looks up the array's device address (once per
  *   device, with that device current); make that first call before starting
@@ -197,6 +246,12 @@ typedef struct aa_stripes_static_args {
 } aa_stripes_static_args_t;
 
 int aa_step2_stripes_static(const aa_stripes_static_args_t *args, void *stream);
+
+/* Status of the bounded device-side waits of the aa_step2_stripes_static calls made so
+ * far on the current device (the word lives at the end of the fixed array and is
+ * cleared by every call): synchronises `stream`, returns AA_OK or
+ * AA_ERR_DEVICE_TIMEOUT.  After a timeout the counts and ids of that call are incomplete. */
+int aa_step2_stripes_static_check_status(void *stream);
 
 /*
  * The block-granular comparator the reference measures anchor attention against:

@@ -8,6 +8,13 @@ OUT_MAX_ABS = 2e-2
 OUT_MEAN_ABS = 1e-3
 
 
+def bf16_step(x: torch.Tensor) -> torch.Tensor:
+    """Distance between neighbouring bf16 values at the magnitude of each element of x
+    (8 significant bits: 2^(floor(log2 |x|) - 7)); zero maps to the smallest step used."""
+    e = torch.floor(torch.log2(x.abs().clamp_min(2.0 ** -120)))
+    return torch.exp2(e - 7)
+
+
 def tie_band(q, k, M, sm_scale, theta, b, block_size=128, step=16):
     """Classify the candidate columns of big block b of one head.
     Returns (sure_in, sure_out, band) as boolean masks over columns

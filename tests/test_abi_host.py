@@ -51,15 +51,21 @@ def test_workspace_layout(lib):
     assert lib.aa_workspace_layout(ctypes.byref(p), ctypes.byref(lay)) == 0
     n = ctypes.c_size_t()
     assert lib.aa_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
-    assert n.value == lay.total_bytes
+    assert n.value == lay.total_bytes == lay.min_bytes + lay.gather_bytes
     offs = [lay.m_off, lay.l_off, lay.acc_off, lay.qpool_off, lay.apool_off, lay.bitmap_off, lay.counts_off,
-            lay.ids_off, lay.status_off, lay.total_bytes]
+            lay.ids_off, lay.status_off, lay.tile_slot_off, lay.gather_off, lay.total_bytes]
     assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
     assert lay.l_off - lay.m_off >= 32 * 131072 * 4
     assert lay.qpool_off - lay.acc_off >= 32 * 131072 * 128 * 4
     assert lay.ids_per_head == sum(b * 2048 - 256 for b in range(1, 64))
     assert lay.status_off - lay.ids_off >= 32 * lay.ids_per_head * 4
-    assert lay.total_bytes < 4 * 2 ** 30       # a few GB at the largest benchmark shape
+    assert lay.min_bytes == lay.gather_off < 4 * 2 ** 30       # a few GB at the largest benchmark shape
+    tiles = 32 * lay.ids_per_head // 128
+    assert lay.gather_off - lay.tile_slot_off >= 4 * tiles
+    assert lay.gather_bytes == min(tiles * 65536, 8 << 30)      # one 64 KB slot per id tile, capped
+    small = _params(N=8192, H=4, Hkv=1)
+    assert lib.aa_workspace_layout(ctypes.byref(small), ctypes.byref(lay)) == 0
+    assert lay.gather_bytes == 4 * (lay.ids_per_head // 128) * 65536
 
 
 @pytest.mark.parametrize("change,code", [
@@ -137,7 +143,8 @@ def test_ctypes_mirrors_match_the_header(tmp_path):
     checks = {
         "aa_params_t": (_lib.AAParams, ["B", "D", "theta", "sm_scale", "q", "out", "q_stride_b", "o_stride_n",
                                         "workspace", "workspace_bytes"]),
-        "aa_workspace_layout_t": (_lib.AALayout, ["m_off", "ids_off", "status_off", "total_bytes", "ids_per_head"]),
+        "aa_workspace_layout_t": (_lib.AALayout, ["m_off", "ids_off", "status_off", "total_bytes", "ids_per_head",
+                                                  "tile_slot_off", "gather_off", "gather_bytes", "min_bytes"]),
         "aa_stripes_static_args_t": (_lib.AAStripesStaticArgs, ["B", "theta", "q", "k_stride_n", "anchors", "ids"]),
         "aa_push_t": (_lib.AAPush, ["n_peers", "out"]),
         "aa_block_sparse_t": (_lib.AABlockSparse, ["B", "max_blocks", "sm_scale", "q", "o_stride_n", "block_index",

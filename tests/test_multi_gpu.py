@@ -28,7 +28,16 @@ def _rank_main(rank, world, port, results):
             for _ in range(3):          # three calls: the pushed output alternates between two copies
                 got = op(Q[:, q_lo:q_hi], K[:, kv_lo:kv_hi], V[:, kv_lo:kv_hi])
             torch.cuda.synchronize()
+            op.check_status()
             ok = ok and got.shape == (1, N, H, 128) and torch.equal(got, want)
+            # the streamed host-buffer path: same assembled output on the device, this rank's
+            # heads back in host memory
+            hq, hk, hv = (t.cpu().pin_memory() for t in (Q[:, q_lo:q_hi], K[:, kv_lo:kv_hi], V[:, kv_lo:kv_hi]))
+            hout = torch.empty((1, q_hi - q_lo, N, 128), dtype=torch.bfloat16).pin_memory()
+            for _ in range(2):
+                full = op.host_call(hq, hk, hv, hout)
+            op.check_status()
+            ok = ok and torch.equal(full, want) and torch.equal(hout.cuda().transpose(1, 2), want[:, :, q_lo:q_hi])
         results[rank] = bool(ok)
         dist.barrier()
     finally:

@@ -78,3 +78,24 @@ def test_decode_and_chunked_prefill_are_dense():
     out, _ = patch.anchor_attention_forward(_module(), Q[:, :, -2048:], K, V, None, scaling=128 ** -0.5,
                                             anchor_attn_fn=never)
     assert (out.transpose(1, 2).float() - dense_causal_attention(Q, K, V)[:, :, -2048:]).abs().max() < 2e-2
+
+
+def test_dense_path_is_chunked_and_equal(monkeypatch):
+    """The dense path runs in query chunks (bounded mask); the chunks together equal one call."""
+    H, Hkv = 2, 1
+    Q, K, V = make_inputs(2048, H, Hkv, seed=13, rope=False)
+    whole = patch._dense_causal(Q[:, :, -700:], K, V, 128 ** -0.5, 2048 - 700)
+    monkeypatch.setattr(patch, "DENSE_CHUNK", 256)
+    parts = patch._dense_causal(Q[:, :, -700:], K, V, 128 ** -0.5, 2048 - 700)
+    assert parts.shape == whole.shape and (parts.float() - whole.float()).abs().max() < 1e-2
+    dense = dense_causal_attention(Q, K, V)[:, :, -700:]
+    assert (parts.float() - dense).abs().max() < 2e-2
+
+
+def test_sliding_window_models_are_refused():
+    from transformers import MistralConfig, MistralForCausalLM
+    cfg = MistralConfig(vocab_size=64, hidden_size=64, intermediate_size=64, num_hidden_layers=1,
+                        num_attention_heads=2, num_key_value_heads=1, head_dim=32, sliding_window=128)
+    model = MistralForCausalLM(cfg)
+    with pytest.raises(ValueError, match="sliding attention window"):
+        patch.patch_model(model, "anchor_attn")
