@@ -77,7 +77,7 @@ class AABlockSparse(ctypes.Structure):
 
 
 class AAPush(ctypes.Structure):
-    _fields_ = [("n_peers", ctypes.c_int32), ("out", ctypes.c_void_p * MAX_PEERS)]
+    _fields_ = [("n_peers", ctypes.c_int32), ("rows_per_peer", ctypes.c_int32), ("out", ctypes.c_void_p * MAX_PEERS)]
 
 
 class AAPeerBarrier(ctypes.Structure):

@@ -222,12 +222,23 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     ta.a = attend_args(p, lay);
     ta.status = ws_ptr<int32_t>(p, lay.status_off);
     ta.n_peers = 0;
+    ta.rows_per_peer = 0;
+    ta.wave = 0;
+    if (MODE == aa::kStripe) {
+        static thread_local int sm_count[64] = {};
+        if (dev >= 0 && dev < 64) {
+            if (!sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+            ta.wave = sm_count[dev];
+        }
+    }
     ta.tile_slot = nullptr;
     ta.gather = nullptr;
+    ta.n_slots = 0;
     ta.list_stride = list_stride;
     for (int i = 0; i < aa::tc::kMaxPeers; ++i) ta.peers[i] = nullptr;
     if (push) {
         ta.n_peers = push->n_peers;
+        ta.rows_per_peer = push->rows_per_peer;
         for (int i = 0; i < push->n_peers; ++i) ta.peers[i] = static_cast<__nv_bfloat16*>(push->out[i]);
     }
     CUtensorMap kmap, vmap;
@@ -263,6 +274,7 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
             if (e != cudaSuccess) return cuda_fail(e, "launch gather pass");
             ta.tile_slot = ga.tile_slot;
             ta.gather = ga.scratch;
+            ta.n_slots = n_slots;
         }
         make_gather_map(&kgmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.k_gather);
         make_gather_map(&vgmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.v_gather);
@@ -458,6 +470,9 @@ int aa_step3_sparse(const aa_params_t* p, void* stream) {
 int aa_step3_sparse_push(const aa_params_t* p, const aa_push_t* push, void* stream) {
     if (!p || !push) return AA_ERR_NULL;
     if (push->n_peers < 1 || push->n_peers > AA_MAX_PEERS) return AA_ERR_SHAPE;
+    if (push->rows_per_peer < 0 || push->rows_per_peer % aa::tc::kTile != 0 ||
+        (push->rows_per_peer > 0 && (int64_t)push->rows_per_peer * push->n_peers < p->N))
+        return AA_ERR_SHAPE;
     for (int i = 0; i < push->n_peers; ++i) {
         if (!push->out[i]) return AA_ERR_NULL;
         if ((uintptr_t)push->out[i] & 15) return AA_ERR_STRIDE;

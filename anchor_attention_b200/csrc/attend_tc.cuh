@@ -75,7 +75,11 @@ struct TcArgs {
     int list_stride;                 // kBlock only: entries reserved per query-tile pair in a.ids
     const int32_t* tile_slot;        // step 3 only: gather slot of every id tile ([B*H, ids_per_head/128]) or NULL
     const uint8_t* gather;           // step 3 only: the 64 KB slots (K image, V image) the gather pass filled
+    int n_slots;                     // step 3 only: slots in `gather`; a table entry beyond it is ignored
+    int wave;                        // CTAs resident at a time (one per SM): CTA i + wave starts about when CTA i ends
     int n_peers;                     // step 3 only: > 0 -> write the output to peers[0 .. n_peers) instead of a.out
+    int rows_per_peer;               // with n_peers > 0: 0 -> every row goes to every peer; > 0 -> row n goes only to
+                                     // peer n / rows_per_peer, at row n % rows_per_peer of that peer's buffer
     __nv_bfloat16* peers[kMaxPeers]; // same element offsets and strides as a.out; may be other GPUs' memory
     int32_t* status;
 };
@@ -406,7 +410,11 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 }
             }
             bar_sync(1 + j, 128);
-            const int64_t tile_off = z * a.osb + h * a.osh + (int64_t)qb * kTile * a.osn;
+            int64_t tile_off = z * a.osb + h * a.osh + (int64_t)qb * kTile * a.osn;
+            // token-sharded destination: the whole tile belongs to one rank (rows_per_peer is a
+            // multiple of the tile height), whose buffer starts at that rank's first row
+            const int owner = ta.rows_per_peer > 0 ? (qb * kTile) / ta.rows_per_peer : 0;
+            if (ta.rows_per_peer > 0) tile_off -= (int64_t)owner * ta.rows_per_peer * a.osn;
             const int ch = r & 15;
 #pragma unroll 4
             for (int it = 0; it < 16; ++it) {
@@ -415,6 +423,8 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 const int64_t off = tile_off + (int64_t)row * a.osn + ch * 8;
                 if (ta.n_peers == 0) {
                     *reinterpret_cast<uint4*>(a.out + off) = val;
+                } else if (ta.rows_per_peer > 0) {
+                    *reinterpret_cast<uint4*>(ta.peers[owner] + off) = val;
                 } else {
                     // head-parallel runs: the rows go straight into every rank's copy of the
                     // assembled output (16-byte stores, a row per 16 threads, over NVLink);
@@ -423,6 +433,46 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 }
             }
         }
+    }
+}
+
+// Which (batch, head, pair of query tiles) CTA `bid` works on.  CTAs that run at the same time
+// share one KV head: its K and V (2 x 256 B x N) stay in L2 while the query heads of the group
+// and their query-tile pairs (heaviest first) walk them.
+struct WorkItem {
+    int pair, z, h, kvh, hz;
+};
+__device__ __forceinline__ WorkItem work_item(const AttendArgs& a, int bid) {
+    const int npairs = a.N / (2 * kTile);
+    const int Hg = a.H / a.Hkv;
+    const int per_kv = Hg * npairs;
+    const int kvz = bid / per_kv, rem = bid % per_kv;
+    WorkItem w;
+    w.pair = npairs - 1 - rem / Hg;
+    w.z = kvz / a.Hkv;
+    w.kvh = kvz % a.Hkv;
+    w.h = w.kvh * Hg + rem % Hg;
+    w.hz = w.z * a.H + w.h;
+    return w;
+}
+
+// Step 3 reads, per CTA, 256 query rows (64 KB), their step-1 state M, L (2 KB) and Acc (128 KB)
+// before it can do anything; with short id lists that is most of a CTA's life.  These lines are
+// asked into L2 ahead of time by `nthreads` threads: by the CTA itself as its first action, and
+// by the CTA that runs one wave earlier once its own loads are issued.
+__device__ __forceinline__ void prefetch_step3_inputs(const AttendArgs& a, const WorkItem& w, int tid, int nthreads,
+                                                      bool with_q) {
+    const int64_t srow0 = (int64_t)w.hz * a.N + (int64_t)w.pair * 2 * kTile;
+    const char* acc = reinterpret_cast<const char*>(a.Acc + srow0 * kD);
+    for (int i = tid; i < 2 * kTile * kD * 4 / 128; i += nthreads) prefetch_l2(acc + (int64_t)i * 128);
+    if (tid < 16) {
+        const float* ml = (tid < 8 ? a.M : a.L) + srow0;
+        prefetch_l2(reinterpret_cast<const char*>(ml) + (tid & 7) * 128);
+    }
+    if (with_q) {
+        const __nv_bfloat16* q = a.q.ptr + w.z * a.q.sb + w.h * a.q.sh + (int64_t)w.pair * 2 * kTile * a.q.sn;
+        for (int i = tid; i < 2 * kTile * 2; i += nthreads)
+            prefetch_l2(reinterpret_cast<const char*>(q + (int64_t)(i >> 1) * a.q.sn) + (i & 1) * 128);
     }
 }
 
@@ -452,15 +502,10 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
 
     // ---- which work item ----
     const int npairs = a.N / (2 * kTile);
-    // CTAs that run at the same time share one KV head: its K and V (2 x 256 B x N) stay in
-    // L2 while the query heads of the group and their query-tile pairs (heaviest first) walk them
-    const int Hg = a.H / a.Hkv;
-    const int per_kv = Hg * npairs;
-    const int kvz = (int)(blockIdx.x / per_kv), rem = (int)(blockIdx.x % per_kv);
-    const int pair = npairs - 1 - rem / Hg;
-    const int z = kvz / a.Hkv, kvh = kvz % a.Hkv;
-    const int h = kvh * Hg + rem % Hg;
-    const int hz = z * a.H + h;
+    const WorkItem wi = work_item(a, (int)blockIdx.x);
+    const int pair = wi.pair, z = wi.z, kvh = wi.kvh, h = wi.h, hz = wi.hz;
+    if (MODE == kStripe) prefetch_step3_inputs(a, wi, tid, kThreads, true);
+    const bool has_next = MODE == kStripe && ta.wave > 0 && blockIdx.x + (unsigned)ta.wave < gridDim.x;
     const int G = a.block * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;
@@ -493,6 +538,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         // (512 bytes in, 256 bytes out per row, coalesced), eight rows in flight per warp, with the
         // arithmetic of the epilogue below.
         constexpr int kWarps = kThreads / 32, kBatch = 8;
+        if (has_next) prefetch_step3_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), tid, kThreads, true);
         for (int row0 = warp; row0 < 2 * kTile; row0 += kWarps * kBatch) {
             float l[kBatch];
             float4 x[kBatch];
@@ -518,9 +564,13 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     uint2 o;
                     o.x = pack_bf16x2(div_l(x[i].x), div_l(x[i].y));
                     o.y = pack_bf16x2(div_l(x[i].z), div_l(x[i].w));
-                    const int64_t off = z * a.osb + h * a.osh + (int64_t)(pair * 2 * kTile + row) * a.osn + lane * 4;
+                    int64_t off = z * a.osb + h * a.osh + (int64_t)(pair * 2 * kTile + row) * a.osn + lane * 4;
                     if (ta.n_peers == 0) {
                         *reinterpret_cast<uint2*>(a.out + off) = o;
+                    } else if (ta.rows_per_peer > 0) {
+                        const int owner = (pair * 2 * kTile + row) / ta.rows_per_peer;
+                        off -= (int64_t)owner * ta.rows_per_peer * a.osn;
+                        *reinterpret_cast<uint2*>(ta.peers[owner] + off) = o;
                     } else {
                         for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint2*>(ta.peers[pr] + off) = o;
                     }
@@ -698,6 +748,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                         const int s0 = t * kTile;
                         run = false;
                         gslot = slotp ? slotp[t] : -1;     // only meaningful when the tile is not a run
+                        if (gslot >= ta.n_slots) gslot = -1;
                         if (s0 + kTile <= count) {
                             row0 = idp[s0];
                             run = (idp[s0 + kTile - 1] - row0) == kTile - 1;
@@ -796,6 +847,9 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     cp_async_mbar_arrive_noinc(kv_full(slot));
                 }
             }
+            // every load of this CTA is under way: ask for the inputs of the CTA one wave later
+            if (has_next)
+                prefetch_step3_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), tid - 9 * 32, kLoaderWarps * 32, true);
             cp_async_wait<0>();
         }
     }

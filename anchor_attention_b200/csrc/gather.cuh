@@ -58,6 +58,9 @@ __global__ void __launch_bounds__(kGatherThreads) gather_tiles_kernel(GatherArgs
     if ((int)blockIdx.x >= ntiles) return;
     const int64_t row_off = id_row_offset(G, a.block, b);
     const int32_t* idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
+    // a full list holds every candidate column in order: all of its tiles are runs (the attention
+    // kernel finds that out by itself and never looks at their slots)
+    if (count == cap && idp[0] == a.block && idp[cap - 1] == b * G - a.block - 1) return;
     int32_t* slots = a.tile_slot + (int64_t)hz * (a.ids_per_head / kTileRows) + row_off / kTileRows;
     const __nv_bfloat16* kbase = a.k.ptr + z * a.k.sb + kvh * a.k.sh;
     const __nv_bfloat16* vbase = a.v.ptr + z * a.v.sb + kvh * a.v.sh;

@@ -137,12 +137,15 @@ class AnchorAttnCall:
         self._call(self._lib.aa_step3_sparse, "anchor_attn.step3_sparse")
         return self.out
 
-    def step3_push(self, peer_ptrs):
+    def step3_push(self, peer_ptrs, rows_per_peer: int = 0):
         """Step 3 that stores every output row to each address in ``peer_ptrs`` (device
         pointers with this call's output strides; may be other GPUs' memory) instead of
-        ``self.out``.  Used by the head-parallel wrapper."""
+        ``self.out``.  With ``rows_per_peer`` > 0 row n goes only to ``peer_ptrs[n // rows_per_peer]``
+        (at row ``n % rows_per_peer`` there): the token-sharded output of a sequence-parallel
+        model.  Used by the head-parallel wrappers."""
         push = _lib.AAPush()
         push.n_peers = len(peer_ptrs)
+        push.rows_per_peer = int(rows_per_peer)
         for i, ptr in enumerate(peer_ptrs):
             push.out[i] = ptr
         with torch.cuda.device(self.Q.device):

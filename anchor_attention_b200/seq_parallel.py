@@ -60,6 +60,14 @@ class SequenceParallelPrefill:
         self.q_lo, self.q_hi, self.kv_lo, self.kv_hi = head_partition(self.H, self.Hkv, self.W, self.rank)
         self._pushed = None
         self.last_call = None
+        self.profile = False          # True: the next call records CUDA events between the stages of every layer
+        self.stage_ms = {}            # stage -> milliseconds summed over the layers of the last profiled call
+
+    def _mark(self, marks, name):
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
 
     # ---- exchanges --------------------------------------------------------------------
     def _tokens_to_heads(self, q, k, v):
@@ -132,6 +140,8 @@ class SequenceParallelPrefill:
         pos = torch.arange(lo, lo + n, device=x.device)[None]
         cos, sin = base.rotary_emb(x, position_ids=pos)
         H, Hkv, D = self.H, self.Hkv, self.D
+        marks = [] if (self.profile and x.is_cuda) else None
+        self._mark(marks, "start")
         for layer in base.layers[: model.config.num_hidden_layers]:
             attn = layer.self_attn
             hn = layer.input_layernorm(x)
@@ -139,10 +149,19 @@ class SequenceParallelPrefill:
             k = attn.k_proj(hn).view(1, n, Hkv, D).transpose(1, 2)
             v = attn.v_proj(hn).view(1, n, Hkv, D)
             q, k = apply_rotary_pos_emb(q, k, cos, sin)
+            self._mark(marks, "norm_qkv_rope")
             Q, K, V = self._tokens_to_heads(q.transpose(1, 2), k.transpose(1, 2), v)
+            self._mark(marks, "tokens_to_heads")
             out = self._attention(Q, K, V, attn.scaling, n)                 # [1, n, H, D]
+            self._mark(marks, "attention_and_heads_to_tokens")
             x = x + attn.o_proj(out.reshape(1, n, H * D))
             x = x + layer.mlp(layer.post_attention_layernorm(x))
+            self._mark(marks, "o_proj_mlp")
+        if marks is not None:
+            torch.cuda.synchronize()
+            self.stage_ms = {}
+            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                self.stage_ms[name] = self.stage_ms.get(name, 0.0) + a.elapsed_time(b)
         logits = None
         vocab = model.config.vocab_size
         if rank == W - 1:

@@ -160,6 +160,10 @@ int aa_validate_lists(const aa_params_t *p, void *stream);
 #define AA_MAX_PEERS 8
 typedef struct aa_push {
     int32_t n_peers;
+    int32_t rows_per_peer;     /* 0: every row goes to every peer (replicated output).
+                                  > 0 (a multiple of 128, n_peers * rows_per_peer >= N): token-sharded
+                                  output -- row n goes only to out[n / rows_per_peer], at row
+                                  n % rows_per_peer of that buffer (whose o_stride_* are p's)      */
     void   *out[AA_MAX_PEERS];
 } aa_push_t;
 int aa_step3_sparse_push(const aa_params_t *p, const aa_push_t *push, void *stream);

@@ -146,7 +146,8 @@ def test_ctypes_mirrors_match_the_header(tmp_path):
         "aa_workspace_layout_t": (_lib.AALayout, ["m_off", "ids_off", "status_off", "total_bytes", "ids_per_head",
                                                   "tile_slot_off", "gather_off", "gather_bytes", "min_bytes"]),
         "aa_stripes_static_args_t": (_lib.AAStripesStaticArgs, ["B", "theta", "q", "k_stride_n", "anchors", "ids"]),
-        "aa_push_t": (_lib.AAPush, ["n_peers", "out"]),
+        "aa_push_t": (_lib.AAPush, ["n_peers", "rows_per_peer", "out"]),
+        "aa_peer_barrier_t": (_lib.AAPeerBarrier, ["n_peers", "epoch", "timeout_ms", "flags", "status"]),
         "aa_block_sparse_t": (_lib.AABlockSparse, ["B", "max_blocks", "sm_scale", "q", "o_stride_n", "block_index",
                                                    "workspace_bytes"]),
     }

@@ -59,3 +59,56 @@ def test_push_and_all_gather_match_single_gpu():
         p.join(timeout=300)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert results.get(0) is True and results.get(1) is True
+
+
+def _seq_rank_main(rank, world, port, results):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    try:
+        from transformers import LlamaConfig, LlamaForCausalLM
+        from anchor_attention_b200 import patch
+        from anchor_attention_b200.seq_parallel import SequenceParallelPrefill
+        torch.manual_seed(0)
+        cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                          num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=8192,
+                          rope_theta=500000.0)
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).cuda().eval()
+        patch.patch_model(model, "anchor_attn", {"theta": 12})
+        g = torch.Generator().manual_seed(3)
+        ids = torch.randint(0, 512, (1, 4096), generator=g).cuda()
+        with torch.no_grad():
+            want = model(input_ids=ids, use_cache=False, logits_to_keep=1).logits.float()
+        ok = True
+        for exchange in ("push", "all_to_all"):
+            sp = SequenceParallelPrefill(model, exchange=exchange)
+            for _ in range(2):
+                got = sp(ids)
+            sp.check_status()
+            diff = (got - want).abs()
+            ok = ok and got.shape == want.shape and float(diff.max()) < 0.15 and float(diff.mean()) < 5e-3
+        results[rank] = bool(ok)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_prefill_matches_single_gpu():
+    """Token-parallel dense layers + head-parallel attention (rows pushed to the token owners, or
+    a second all-to-all) on two GPUs against the same tiny model run on one GPU."""
+    import torch.multiprocessing as mp
+    from anchor_attention_b200 import _lib
+    _lib.load()
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = 29900 + os.getpid() % 100
+    procs = [ctx.Process(target=_seq_rank_main, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert results.get(0) is True and results.get(1) is True
