@@ -1,7 +1,7 @@
 """B200-native anchor attention: the reference's ``anchor_attn`` prefill operator
 backed by hand-written sm_100a CUDA kernels behind a C ABI."""
 from .ops import (AnchorAttnCall, anchor_attn, anchor_attn_host, anchor_attn_without_anchor,
-                  launches_per_forward)
+                  dense_causal_attention, launches_per_forward)
 
 
 def __getattr__(name):
@@ -12,4 +12,4 @@ def __getattr__(name):
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 __all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
-           "launches_per_forward", "block_sparse_attention"]
+           "dense_causal_attention", "launches_per_forward", "block_sparse_attention"]

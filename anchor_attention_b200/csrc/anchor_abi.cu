@@ -205,9 +205,15 @@ int make_gather_map(CUtensorMap* map, const void* ptr, int64_t sb, int64_t sh, i
     return AA_OK;
 }
 
+// Dense causal variant of the block mode: the query tensor holds the last q_rows positions of a
+// kv_rows-long sequence (p->N is q_rows rounded up to 256 and only sizes the grid).
+struct DenseTail {
+    int q_rows, kv_rows;
+};
+
 template <int MODE>
 int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st,
-                     const aa_push_t* push = nullptr, int list_stride = 0) {
+                     const aa_push_t* push = nullptr, int list_stride = 0, const DenseTail* dense = nullptr) {
     static thread_local int configured_dev[3] = {-1, -1, -1};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -224,7 +230,18 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     ta.n_peers = 0;
     ta.rows_per_peer = 0;
     ta.wave = 0;
-    if (MODE == aa::kStripe) {
+    ta.dense = 0;
+    ta.q_rows = p->N;
+    ta.q_off = 0;
+    ta.kv_blocks = p->N / aa::tc::kTile;
+    const int kv_rows = dense ? dense->kv_rows : p->N;
+    if (dense) {
+        ta.dense = 1;
+        ta.q_rows = dense->q_rows;
+        ta.q_off = dense->kv_rows - dense->q_rows;
+        ta.kv_blocks = (dense->kv_rows + aa::tc::kTile - 1) / aa::tc::kTile;
+    }
+    if (MODE != aa::kBlock) {
         static thread_local int sm_count[64] = {};
         if (dev >= 0 && dev < 64) {
             if (!sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
@@ -242,10 +259,10 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
         for (int i = 0; i < push->n_peers; ++i) ta.peers[i] = static_cast<__nv_bfloat16*>(push->out[i]);
     }
     CUtensorMap kmap, vmap;
-    int rc = make_kv_map(&kmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.kpos_n,
+    int rc = make_kv_map(&kmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, kv_rows, &ta.kpos_n,
                          &ta.kpos_h, &ta.kpos_b);
     if (rc) return rc;
-    rc = make_kv_map(&vmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.vpos_n,
+    rc = make_kv_map(&vmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, kv_rows, &ta.vpos_n,
                      &ta.vpos_h, &ta.vpos_b);
     if (rc) return rc;
     CUtensorMap kgmap, vgmap;
@@ -795,6 +812,43 @@ int aa_block_sparse_attend(const aa_block_sparse_t* a, void* stream) {
     lay.ids_per_head = (int64_t)bl.npairs * bl.list_stride;
     lay.total_bytes = bl.total_bytes;
     return launch_attend_tc<aa::kBlock>(&p, lay, st, nullptr, bl.list_stride);
+}
+
+int aa_dense_causal_attend(const aa_dense_causal_t* a, void* stream) {
+    if (!a) return AA_ERR_NULL;
+    if (a->B <= 0 || a->H <= 0 || a->Hkv <= 0 || a->Nq <= 0 || a->Nkv < a->Nq || a->H % a->Hkv != 0) return AA_ERR_SHAPE;
+    if (a->D != 128) return AA_ERR_HEAD_DIM;
+    if (a->dtype != AA_BF16) return AA_ERR_DTYPE;
+    if ((int64_t)a->Nkv * a->H * a->B > (int64_t)1 << 40 || a->Nkv / aa::tc::kTile >= (int)aa::kBlockIdMask)
+        return AA_ERR_TOO_LARGE;
+    if (!a->q || !a->k || !a->v || !a->out || !a->status) return AA_ERR_NULL;
+    const int64_t strides[] = {a->q_stride_b, a->q_stride_h, a->q_stride_n, a->k_stride_b, a->k_stride_h, a->k_stride_n,
+                               a->v_stride_b, a->v_stride_h, a->v_stride_n, a->o_stride_b, a->o_stride_h, a->o_stride_n};
+    for (int64_t s : strides)
+        if (!stride_ok(s)) return AA_ERR_STRIDE;
+    if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15) return AA_ERR_STRIDE;
+    if ((uintptr_t)a->status & 15) return AA_ERR_STRIDE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(a->status, 0, 4 * sizeof(int32_t), st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(status)");
+    // the attention kernel takes the operator's argument block: fill in what the dense variant reads
+    aa_params_t p;
+    memset(&p, 0, sizeof(p));
+    p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.D = a->D;
+    p.N = (a->Nq + 2 * aa::tc::kTile - 1) / (2 * aa::tc::kTile) * (2 * aa::tc::kTile);      // grid: pairs of query tiles
+    p.block_size = 128; p.step = 16; p.dtype = a->dtype;
+    p.sm_scale = a->sm_scale;
+    p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out;
+    p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h; p.q_stride_n = a->q_stride_n;
+    p.k_stride_b = a->k_stride_b; p.k_stride_h = a->k_stride_h; p.k_stride_n = a->k_stride_n;
+    p.v_stride_b = a->v_stride_b; p.v_stride_h = a->v_stride_h; p.v_stride_n = a->v_stride_n;
+    p.o_stride_b = a->o_stride_b; p.o_stride_h = a->o_stride_h; p.o_stride_n = a->o_stride_n;
+    p.workspace = a->status;                     // only the status words are used
+    p.workspace_bytes = 4 * sizeof(int32_t);
+    aa_workspace_layout_t lay;
+    memset(&lay, 0, sizeof(lay));
+    DenseTail dt{a->Nq, a->Nkv};
+    return launch_attend_tc<aa::kBlock>(&p, lay, st, nullptr, 0, &dt);
 }
 
 int aa_block_sparse_check_status(const aa_block_sparse_t* a, void* stream) {

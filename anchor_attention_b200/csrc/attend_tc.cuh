@@ -73,6 +73,10 @@ struct TcArgs {
     int vpos_n, vpos_h, vpos_b;
     int k_gather, v_gather;          // 1: the 2-D row-gather tensor map of K / V is usable
     int list_stride;                 // kBlock only: entries reserved per query-tile pair in a.ids
+    // kBlock, dense causal variant (the tail of a prefill, a later prefill chunk): no lists; the query
+    // rows are the LAST q_rows positions of a kv_rows-long sequence (a.N = the rows rounded up to
+    // 256), row i attends every key up to position q_off + i, q_off = kv_rows - q_rows
+    int dense, q_rows, q_off, kv_blocks;
     const int32_t* tile_slot;        // step 3 only: gather slot of every id tile ([B*H, ids_per_head/128]) or NULL
     const uint8_t* gather;           // step 3 only: the 64 KB slots (K image, V image) the gather pass filled
     int n_slots;                     // step 3 only: slots in `gather`; a table entry beyond it is ignored
@@ -92,6 +96,17 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * kSlabBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
+// The un-normalised fp32 output of step 1 (the reference's Acc_buffer, anchor_step_1_2_v2.py:176)
+// is private to steps 1 and 3, and both touch it with one thread per row.  It is therefore kept in
+// tiles of 128 rows (64 KB, tile t = rows 128t .. 128t+127 of a (batch, head)), each tile
+// chunk-major: the 16-byte chunk k (columns 4k .. 4k+3) of all 128 rows is one 2 KB run, row r at
+// offset 16 r.  A warp whose lane r reads or writes chunk k of row r then touches 512 contiguous
+// bytes, instead of 32 lines 512 bytes apart as it would with row-major rows.
+__device__ __forceinline__ float* acc_tile(float* acc, int64_t hz, int N, int qb) {
+    return acc + ((int64_t)hz * N + (int64_t)qb * kTile) * kD;
+}
+__device__ __forceinline__ int acc_chunk_off(int k, int r) { return k * (kTile * 4) + r * 4; }      // in floats
+
 __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int pos_n, int pos_h,
                                          int pos_b, int row, int head, int z) {
     const int c0 = pos_n == 0 ? row : (pos_h == 0 ? head : z);
@@ -99,6 +114,14 @@ __device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, u
     const int c2 = pos_n == 2 ? row : (pos_h == 2 ? head : z);
     tma_load_4d(dst, map, bar, 0, c0, c1, c2);
     tma_load_4d(dst + kSlabBytes, map, bar, 64, c0, c1, c2);
+}
+
+// Entry t of a block-mode CTA's tile list: read from the merged list, or, in the dense causal
+// variant, made up on the spot -- key block t, attended by both query tiles up to the first
+// tile's last block and by the second tile alone beyond it.
+__device__ __forceinline__ uint32_t block_entry(const TcArgs& ta, const int32_t* list, int t, int dense_last0) {
+    if (ta.dense) return (uint32_t)t | ((t <= dense_last0 ? 3u : 2u) << kBlockFlagShift);
+    return (uint32_t)list[t];
 }
 
 // What the softmax warps need to know about their CTA: where the tiles and barriers are.
@@ -110,6 +133,7 @@ struct SoftmaxCtx {
     uint32_t q_full[2], s_full[2], o_done[2], p_part[2][4];
     int pair, z, h, hz, ntiles, n_init, local_start, count;
     const int32_t* list;             // kBlock only: the pair's tile list
+    int dense_last0;                 // kBlock, dense variant: last key block of the pair's first query tile
 };
 
 // The softmax role of warps 0-7 (see the file header): thread r of tile j owns query row r.
@@ -147,7 +171,10 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int id = r + 128 * i;
-            raws[i] = *reinterpret_cast<const uint4*>(qbase + (int64_t)(id >> 4) * a.q.sn + (id & 15) * 8);
+            if (MODE == kBlock && qb * kTile + (id >> 4) >= ta.q_rows)
+                raws[i] = make_uint4(0u, 0u, 0u, 0u);          // padding rows of the dense variant
+            else
+                raws[i] = *reinterpret_cast<const uint4*>(qbase + (int64_t)(id >> 4) * a.q.sn + (id & 15) * 8);
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -184,20 +211,22 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         m_true = m_ref = a.M[srow];
         l = a.L[srow];
         if (ntiles > 0) {
-            const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
+            const float* tile_acc = acc_tile(a.Acc, hz, a.N, qb);
+            // all 32 loads of the row are issued before the first tensor-memory store (the stores
+            // are ordered against memory operations, so loads behind one would wait for it)
+            uint32_t v[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float4 x = src[c * 8 + i];
-                    v[4 * i] = __float_as_uint(x.x);
-                    v[4 * i + 1] = __float_as_uint(x.y);
-                    v[4 * i + 2] = __float_as_uint(x.z);
-                    v[4 * i + 3] = __float_as_uint(x.w);
+                    const float4 x = *reinterpret_cast<const float4*>(tile_acc + acc_chunk_off(c * 8 + i, r));
+                    v[c][4 * i] = __float_as_uint(x.x);
+                    v[c][4 * i + 1] = __float_as_uint(x.y);
+                    v[c][4 * i + 2] = __float_as_uint(x.z);
+                    v[c][4 * i + 3] = __float_as_uint(x.w);
                 }
-                tmem_st32(tO + c * 32, v);
-            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st32(tO + c * 32, v[c]);
             tmem_wait_st();
         }
     } else {
@@ -212,13 +241,13 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar);
     };
-    uint32_t entry_next = (MODE == kBlock && ntiles > 0) ? (uint32_t)cx.list[0] : 0u;
+    uint32_t entry_next = (MODE == kBlock && ntiles > 0) ? block_entry(ta, cx.list, 0, cx.dense_last0) : 0u;
     int mine = 0;        // kBlock: tiles of this query tile so far (the MMA warp counts the same way)
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
         const uint32_t entry = entry_next;
         if (MODE == kBlock) {
-            if (t + 1 < ntiles) entry_next = (uint32_t)cx.list[t + 1];
+            if (t + 1 < ntiles) entry_next = block_entry(ta, cx.list, t + 1, cx.dense_last0);
             // a block of the other query tile only: no S is produced for this one, nothing to do
             if (!((entry >> (kBlockFlagShift + j)) & 1u)) continue;
         }
@@ -244,12 +273,15 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                             sv[c][i] = __float_as_uint(__uint_as_float(sv[c][i]) + -1e6f);
             }
         } else if (MODE == kBlock) {
-            if ((int)(entry & kBlockIdMask) == qb) {      // the tile's own block: keys after the query row
+            // keys after the query row: d = position of the tile's first query row minus the block's
+            // first key (0 on the tile's own block of the comparator; any value in the dense variant)
+            const int d = ta.q_off + (qb - (int)(entry & kBlockIdMask)) * kTile;
+            if (d < kTile - 1) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i > r) sv[c][i] = __float_as_uint(-INFINITY);
+                        if (c * 32 + i > r + d) sv[c][i] = __float_as_uint(-INFINITY);
             }
         } else {
             const int valid = count - t * kTile;
@@ -323,41 +355,25 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     }
     if (MODE == kWindow) {
         // All 128 threads of the tile get here; they first agree that none of them gave up.  The fp32
-        // accumulator rows (512 bytes each) are staged in shared memory (the tile's query buffer, which
-        // no MMA reads any more), 64 columns at a time, and written out as whole 256-byte pieces by
-        // consecutive threads.
+        // accumulator goes out in the tile layout of acc_tile(): thread r stores the 16-byte chunks
+        // of its row, a warp 512 contiguous bytes per instruction, straight from registers.
         const bool all_ok = bar_and(1 + j, 128, ok);
         if (all_ok) {
             const float sc = fast_exp2(m_ref - m_true);
             a.M[srow] = m_true;
             a.L[srow] = l * sc;
-            uint8_t* stage = smem + j * kTileBytes;
-            float* tile_acc = a.Acc + ((int64_t)hz * a.N + (int64_t)qb * kTile) * kD;
-            const int ch = r & 15;
+            float* tile_acc = acc_tile(a.Acc, hz, a.N, qb);
 #pragma unroll 1
-            for (int hcol = 0; hcol < 2; ++hcol) {
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tO + hcol * 64 + c * 32, v);
-                    tmem_wait_ld();
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tO + c * 32, v);
+                tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 x = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
-                                                     __uint_as_float(v[4 * i + 2]) * sc,
-                                                     __uint_as_float(v[4 * i + 3]) * sc);
-                        // row r, 16-byte chunk c*8+i of this 256-byte half row, at chunk slot (chunk ^ (r & 7))
-                        *reinterpret_cast<float4*>(stage + r * kRowBytes + (((c * 8 + i) ^ (r & 7)) << 4)) = x;
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    const float4 x = make_float4(__uint_as_float(v[4 * i]) * sc, __uint_as_float(v[4 * i + 1]) * sc,
+                                                 __uint_as_float(v[4 * i + 2]) * sc, __uint_as_float(v[4 * i + 3]) * sc);
+                    *reinterpret_cast<float4*>(tile_acc + acc_chunk_off(c * 8 + i, r)) = x;
                 }
-                bar_sync(1 + j, 128);
-#pragma unroll 4
-                for (int it = 0; it < 16; ++it) {
-                    const int row = it * 8 + (r >> 4);
-                    const float4 x = *reinterpret_cast<const float4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
-                    *reinterpret_cast<float4*>(tile_acc + (int64_t)row * kD + hcol * 64 + ch * 4) = x;
-                }
-                bar_sync(1 + j, 128);
             }
         }
     } else {
@@ -368,7 +384,6 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
         const bool all_ok = bar_and(1 + j, 128, ok);
         if (all_ok) {
             uint8_t* stage = smem + j * kTileBytes;
-            const float4* src = reinterpret_cast<const float4*>(a.Acc + srow * kD);
             // acc / l, correctly rounded: one IEEE reciprocal of l per row, then the quotient estimate
             // acc * (1/l) corrected once with the exact remainder (two fused multiply-adds).  Equals the
             // IEEE quotient for normal operands, at a third of the instructions of a division.
@@ -385,18 +400,9 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 if (ntiles > 0) {
                     tmem_ld32(tO + c * 32, v);
                     tmem_wait_ld();
-                } else if (MODE == kBlock) {
+                } else {                 // block mode with an empty list (step 3 never gets here without tiles)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0u;
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 x = src[c * 8 + i];
-                        v[4 * i] = __float_as_uint(x.x);
-                        v[4 * i + 1] = __float_as_uint(x.y);
-                        v[4 * i + 2] = __float_as_uint(x.z);
-                        v[4 * i + 3] = __float_as_uint(x.w);
-                    }
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -421,6 +427,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
                 const int row = it * 8 + (r >> 4);
                 const uint4 val = *reinterpret_cast<const uint4*>(stage + row * kRowBytes + ((ch ^ (row & 7)) << 4));
                 const int64_t off = tile_off + (int64_t)row * a.osn + ch * 8;
+                if (MODE == kBlock && qb * kTile + row >= ta.q_rows) continue;      // padding rows of the dense variant
                 if (ta.n_peers == 0) {
                     *reinterpret_cast<uint4*>(a.out + off) = val;
                 } else if (ta.rows_per_peer > 0) {
@@ -456,23 +463,26 @@ __device__ __forceinline__ WorkItem work_item(const AttendArgs& a, int bid) {
     return w;
 }
 
-// Step 3 reads, per CTA, 256 query rows (64 KB), their step-1 state M, L (2 KB) and Acc (128 KB)
-// before it can do anything; with short id lists that is most of a CTA's life.  These lines are
-// asked into L2 ahead of time by `nthreads` threads: by the CTA itself as its first action, and
-// by the CTA that runs one wave earlier once its own loads are issued.
-__device__ __forceinline__ void prefetch_step3_inputs(const AttendArgs& a, const WorkItem& w, int tid, int nthreads,
-                                                      bool with_q) {
+// A CTA reads 256 query rows (64 KB) and, in step 3, their step-1 state M, L (2 KB) and Acc
+// (128 KB) before it can do anything; with short id lists that is most of a CTA's life.  These ranges are
+// asked into L2 ahead of time with bulk prefetches issued by one warp (`lane` of it): by the CTA
+// itself as its first action, and by the CTA that runs one wave earlier once its own loads are
+// issued, so that the fetches overlap that CTA's arithmetic and output.
+__device__ __forceinline__ void prefetch_inputs(const AttendArgs& a, const WorkItem& w, int lane, bool with_state) {
     const int64_t srow0 = (int64_t)w.hz * a.N + (int64_t)w.pair * 2 * kTile;
-    const char* acc = reinterpret_cast<const char*>(a.Acc + srow0 * kD);
-    for (int i = tid; i < 2 * kTile * kD * 4 / 128; i += nthreads) prefetch_l2(acc + (int64_t)i * 128);
-    if (tid < 16) {
-        const float* ml = (tid < 8 ? a.M : a.L) + srow0;
-        prefetch_l2(reinterpret_cast<const char*>(ml) + (tid & 7) * 128);
+    if (!with_state) {
+        // step 1 starts from an empty state: only the query rows
+    } else if (lane < 4) {
+        // the state of the pair's two tiles is contiguous: 4 x 32 KB
+        bulk_prefetch_l2(reinterpret_cast<const char*>(a.Acc + srow0 * kD) + lane * 32768, 32768);
+    } else if (lane < 6) {
+        bulk_prefetch_l2((lane == 4 ? a.M : a.L) + srow0, 2 * kTile * 4);
     }
-    if (with_q) {
-        const __nv_bfloat16* q = a.q.ptr + w.z * a.q.sb + w.h * a.q.sh + (int64_t)w.pair * 2 * kTile * a.q.sn;
-        for (int i = tid; i < 2 * kTile * 2; i += nthreads)
-            prefetch_l2(reinterpret_cast<const char*>(q + (int64_t)(i >> 1) * a.q.sn) + (i & 1) * 128);
+    const __nv_bfloat16* q = a.q.ptr + w.z * a.q.sb + w.h * a.q.sh + (int64_t)w.pair * 2 * kTile * a.q.sn;
+    if (a.q.sn == kD) {
+        if (lane >= 6 && lane < 8) bulk_prefetch_l2(q + (lane - 6) * kTile * kD, kTileBytes);
+    } else {
+        for (int r = lane; r < 2 * kTile; r += 32) bulk_prefetch_l2(q + (int64_t)r * a.q.sn, kRowBytes);
     }
 }
 
@@ -504,13 +514,12 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     const int npairs = a.N / (2 * kTile);
     const WorkItem wi = work_item(a, (int)blockIdx.x);
     const int pair = wi.pair, z = wi.z, kvh = wi.kvh, h = wi.h, hz = wi.hz;
-    if (MODE == kStripe) prefetch_step3_inputs(a, wi, tid, kThreads, true);
-    const bool has_next = MODE == kStripe && ta.wave > 0 && blockIdx.x + (unsigned)ta.wave < gridDim.x;
+    const bool has_next = MODE != kBlock && ta.wave > 0 && blockIdx.x + (unsigned)ta.wave < gridDim.x;
     const int G = a.block * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;
 
-    int ntiles, n_init = 0, local_start = 0, count = 0;
+    int ntiles, n_init = 0, local_start = 0, count = 0, dense_last0 = 0;
     const int32_t* idp = nullptr;
     const int32_t* slotp = nullptr;      // step 3: gather slots of this list's tiles
     if (MODE == kWindow) {
@@ -519,6 +528,10 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         local_start = max(b * G, init_end);
         n_init = init_end / kTile;
         ntiles = n_init + (end - local_start) / kTile;
+    } else if (MODE == kBlock && ta.dense) {
+        // key blocks 0 .. the one that holds the last position a row of the tile may attend
+        dense_last0 = min((ta.q_off + (2 * pair) * kTile + kTile - 1) / kTile, ta.kv_blocks - 1);
+        ntiles = min((ta.q_off + (2 * pair + 1) * kTile + kTile - 1) / kTile, ta.kv_blocks - 1) + 1;
     } else if (MODE == kBlock) {
         count = a.counts[(int64_t)hz * npairs + pair];          // entries of the pair's merged tile list
         ntiles = count;
@@ -530,50 +543,59 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)a.block * (b - 1));
         idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
         if (ta.tile_slot) slotp = ta.tile_slot + (int64_t)hz * (a.ids_per_head / kTile) + row_off / kTile;
+        if (warp == 0) prefetch_inputs(a, wi, lane, true);        // this CTA's own inputs, in case nobody asked before
     }
 
     if (MODE == kStripe && ntiles == 0) {
         // Nothing selected for these rows (always so in the first big block): the output is step 1's
-        // state normalised, acc / l.  No tensor memory, no barriers: every warp streams whole rows
-        // (512 bytes in, 256 bytes out per row, coalesced), eight rows in flight per warp, with the
-        // arithmetic of the epilogue below.
-        constexpr int kWarps = kThreads / 32, kBatch = 8;
-        if (has_next) prefetch_step3_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), tid, kThreads, true);
-        for (int row0 = warp; row0 < 2 * kTile; row0 += kWarps * kBatch) {
-            float l[kBatch];
-            float4 x[kBatch];
+        // state normalised, acc / l, with the arithmetic of the epilogue.  No tensor memory, no
+        // barriers.  A warp takes 32 rows x 32 columns at a time: lane r reads the eight 16-byte
+        // chunks of its row (512 contiguous bytes per instruction in the tile layout), divides,
+        // and the warp turns its 32 x 64 bytes of bf16 through shared memory so that the rows go
+        // out as 64-byte pieces from four consecutive lanes.
+        constexpr int kWarps = kThreads / 32;
+        if (has_next && warp == kWarps - 1) prefetch_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), lane, true);
+        uint8_t* wbuf = smem + warp * 2048;
+        for (int u = warp; u < 32; u += kWarps) {
+            const int row = (u >> 2) * 32 + lane, quarter = u & 3;          // row inside the pair's 256 rows
+            const int64_t srow = (int64_t)hz * a.N + pair * 2 * kTile + row;
+            const float* tile_acc = acc_tile(a.Acc, hz, a.N, 2 * pair + (row >> 7));
+            const float li = a.L[srow];
+            float4 x[8];
 #pragma unroll
-            for (int i = 0; i < kBatch; ++i) {
-                const int row = row0 + i * kWarps;
-                if (row < 2 * kTile) {
-                    const int64_t srow = (int64_t)hz * a.N + pair * 2 * kTile + row;
-                    l[i] = a.L[srow];
-                    x[i] = reinterpret_cast<const float4*>(a.Acc + srow * kD)[lane];
-                }
+            for (int i = 0; i < 8; ++i)
+                x[i] = *reinterpret_cast<const float4*>(tile_acc + acc_chunk_off(quarter * 8 + i, row & 127));
+            const float rl = __frcp_rn(li);
+            auto div_l = [&](float v) {
+                const float q0 = __fmul_rn(v, rl);
+                const float rem = __fmaf_rn(-q0, li, v);
+                return __fmaf_rn(rem, rl, q0);
+            };
+            __syncwarp();                                                   // the previous unit's rows have been read
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint4 o4;
+                o4.x = pack_bf16x2(div_l(x[2 * i].x), div_l(x[2 * i].y));
+                o4.y = pack_bf16x2(div_l(x[2 * i].z), div_l(x[2 * i].w));
+                o4.z = pack_bf16x2(div_l(x[2 * i + 1].x), div_l(x[2 * i + 1].y));
+                o4.w = pack_bf16x2(div_l(x[2 * i + 1].z), div_l(x[2 * i + 1].w));
+                *reinterpret_cast<uint4*>(wbuf + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = o4;
             }
+            __syncwarp();
 #pragma unroll
-            for (int i = 0; i < kBatch; ++i) {
-                const int row = row0 + i * kWarps;
-                if (row < 2 * kTile) {
-                    const float li = l[i], rl = __frcp_rn(li);
-                    auto div_l = [&](float v) {
-                        const float q0 = __fmul_rn(v, rl);
-                        const float rem = __fmaf_rn(-q0, li, v);
-                        return __fmaf_rn(rem, rl, q0);
-                    };
-                    uint2 o;
-                    o.x = pack_bf16x2(div_l(x[i].x), div_l(x[i].y));
-                    o.y = pack_bf16x2(div_l(x[i].z), div_l(x[i].w));
-                    int64_t off = z * a.osb + h * a.osh + (int64_t)(pair * 2 * kTile + row) * a.osn + lane * 4;
-                    if (ta.n_peers == 0) {
-                        *reinterpret_cast<uint2*>(a.out + off) = o;
-                    } else if (ta.rows_per_peer > 0) {
-                        const int owner = (pair * 2 * kTile + row) / ta.rows_per_peer;
-                        off -= (int64_t)owner * ta.rows_per_peer * a.osn;
-                        *reinterpret_cast<uint2*>(ta.peers[owner] + off) = o;
-                    } else {
-                        for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint2*>(ta.peers[pr] + off) = o;
-                    }
+            for (int it = 0; it < 4; ++it) {
+                const int rr = it * 8 + (lane >> 2), cc = lane & 3;
+                const uint4 val = *reinterpret_cast<const uint4*>(wbuf + rr * 64 + ((cc ^ ((rr >> 1) & 3)) << 4));
+                const int grow = pair * 2 * kTile + (u >> 2) * 32 + rr;      // row inside the head
+                int64_t off = z * a.osb + h * a.osh + (int64_t)grow * a.osn + quarter * 32 + cc * 8;
+                if (ta.n_peers == 0) {
+                    *reinterpret_cast<uint4*>(a.out + off) = val;
+                } else if (ta.rows_per_peer > 0) {
+                    const int owner = grow / ta.rows_per_peer;
+                    off -= (int64_t)owner * ta.rows_per_peer * a.osn;
+                    *reinterpret_cast<uint4*>(ta.peers[owner] + off) = val;
+                } else {
+                    for (int pr = 0; pr < ta.n_peers; ++pr) *reinterpret_cast<uint4*>(ta.peers[pr] + off) = val;
                 }
             }
         }
@@ -620,6 +642,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
         sc.ntiles = ntiles; sc.n_init = n_init; sc.local_start = local_start; sc.count = count;
         sc.list = idp;
+        sc.dense_last0 = dense_last0;
         softmax_role<MODE>(ta, sc, tid);
     } else {
         setmaxnreg_dec<kOtherRegs>();
@@ -662,8 +685,8 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             // The list entries are read two tiles ahead.
             uint32_t e_cur = 0xC0000000u, e_next = 0xC0000000u;
             if (MODE == kBlock) {
-                e_cur = (uint32_t)idp[0];
-                e_next = ntiles > 1 ? (uint32_t)idp[1] : 0u;
+                e_cur = block_entry(ta, idp, 0, dense_last0);
+                e_next = ntiles > 1 ? block_entry(ta, idp, 1, dense_last0) : 0u;
             }
             auto attends = [&](uint32_t e, int j) { return MODE != kBlock || ((e >> (kBlockFlagShift + j)) & 1u) != 0u; };
             int done[2] = {0, 0};          // P V products issued per query tile
@@ -684,7 +707,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int nv = 2 * t + 1, nk = 2 * t + 2;
                 uint32_t e_after = 0u;
-                if (MODE == kBlock && t + 2 < ntiles) e_after = (uint32_t)idp[t + 2];
+                if (MODE == kBlock && t + 2 < ntiles) e_after = block_entry(ta, idp, t + 2, dense_last0);
                 ok = wait_all(kv_full(nv % kStages), (nv / kStages) & 1);
                 if (!ok) break;
                 fence_proxy_async();
@@ -743,7 +766,7 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     if (MODE == kWindow) {
                         row0 = (t < n_init) ? t * kTile : local_start + (t - n_init) * kTile;
                     } else if (MODE == kBlock) {
-                        row0 = (int)((uint32_t)idp[t] & kBlockIdMask) * kTile;
+                        row0 = (int)(block_entry(ta, idp, t, dense_last0) & kBlockIdMask) * kTile;
                     } else {
                         const int s0 = t * kTile;
                         run = false;
@@ -848,8 +871,8 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                 }
             }
             // every load of this CTA is under way: ask for the inputs of the CTA one wave later
-            if (has_next)
-                prefetch_step3_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), tid - 9 * 32, kLoaderWarps * 32, true);
+            if (has_next && lw == kLoaderWarps - 1)
+                prefetch_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), lane, MODE == kStripe);
             cp_async_wait<0>();
         }
     }

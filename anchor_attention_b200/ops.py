@@ -21,7 +21,7 @@ import torch
 from . import _lib
 
 __all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
-           "launches_per_forward"]
+           "dense_causal_attention", "launches_per_forward"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 _NVTX = os.environ.get("ANCHOR_ATTN_NVTX", "0") == "1"
@@ -183,8 +183,11 @@ class AnchorAttnCall:
 
     @property
     def Acc(self):
-        return self._view(self.layout.acc_off, self.B * self.H * self.N * self.D, torch.float32).view(
-            self.B, self.H, self.N, self.D)
+        """Step 1's un-normalised output as a [B,H,N,D] tensor (a copy).  In the workspace it is kept
+        in tiles of 128 rows, each tile chunk-major: [B, H, N/128, D/4 chunks, 128 rows, 4]."""
+        raw = self._view(self.layout.acc_off, self.B * self.H * self.N * self.D, torch.float32).view(
+            self.B, self.H, self.N // 128, self.D // 4, 128, 4)
+        return raw.permute(0, 1, 2, 4, 3, 5).reshape(self.B, self.H, self.N, self.D)
 
     @property
     def qpool(self):
@@ -321,6 +324,47 @@ def anchor_attn_host(Q, K, V, out=None,
             drained[i].record(s_out)
     main.wait_stream(s_out)
     main.synchronize()
+    return out
+
+
+_dense_status: Dict[int, torch.Tensor] = {}
+
+
+def dense_causal_attention(query, key, value, scaling: float = None, out: Optional[torch.Tensor] = None):
+    """Dense causal attention of the LAST ``q`` positions of a ``kv``-long sequence on the library's
+    own attention kernel: query [B,H,q,D], key/value [B,Hkv,kv,D] (kv >= q), bf16 CUDA tensors,
+    D = 128; row i attends keys 0 .. kv - q + i.  Returns [B,H,q,D] (``out`` may be a strided view,
+    e.g. of token-major memory).  The path the reference sends to flash-attn for the tail of a
+    prefill and for later chunks (anchor_attn/src/modules/llama/anchor_attention.py:76-88, 101-113).
+    A prefill kernel (128-row tiles): single-token decode should keep using a split-KV library kernel."""
+    lib = _lib.load()
+    assert query.is_cuda and key.is_cuda and value.is_cuda, "dense_causal_attention takes CUDA tensors (no CPU path)"
+    assert query.dtype == torch.bfloat16 and key.dtype == query.dtype and value.dtype == query.dtype
+    B, H, nq, D = query.shape
+    Hkv, nkv = key.shape[1], key.shape[2]
+    assert D == 128 and key.shape == value.shape and key.shape[0] == B and key.shape[3] == D
+    assert H % Hkv == 0 and nkv >= nq >= 1
+    q, k, v = _usable(query), _usable(key), _usable(value)
+    if out is None:
+        out = torch.empty((B, H, nq, D), dtype=query.dtype, device=query.device)
+    dev = query.device.index if query.device.index is not None else torch.cuda.current_device()
+    status = _dense_status.get(dev)
+    if status is None:
+        status = _dense_status[dev] = torch.zeros(4, dtype=torch.int32, device=query.device)
+    a = _lib.AADenseCausal()
+    a.B, a.H, a.Hkv, a.Nq, a.Nkv, a.D = B, H, Hkv, nq, nkv, D
+    a.dtype = _lib.AA_BF16
+    a.sm_scale = float(scaling) if scaling else 0.0
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", out)):
+        setattr(a, f"{name}_stride_b", t.stride(0))
+        setattr(a, f"{name}_stride_h", t.stride(1))
+        setattr(a, f"{name}_stride_n", t.stride(2))
+    a.status = status.data_ptr()
+    with torch.cuda.device(query.device):
+        rc = lib.aa_dense_causal_attend(ctypes.byref(a), ctypes.c_void_p(torch.cuda.current_stream(query.device).cuda_stream))
+    if rc != _lib.AA_OK:
+        raise RuntimeError(f"dense_causal_attention: {_lib.error_text(rc)}")
     return out
 
 

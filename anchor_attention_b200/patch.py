@@ -75,17 +75,23 @@ def patch_model_config(model, pattern: str, cfg=None):
     return cfg
 
 
-DENSE_CHUNK = 4096   # queries per call of the dense path: bounds the boolean mask to 4096 x kv_len
+DENSE_CHUNK = 4096   # queries per SDPA call of the dense path: bounds the boolean mask to 4096 x kv_len
+DENSE_KERNEL_MIN_Q = 16   # from this many queries on the dense path runs on the library's own kernel
 
 
 def _dense_causal(query, key, value, scaling, q_offset):
     """Dense causal attention of ``query`` (positions q_offset .. q_offset+q-1) over
-    all keys; the comparator path for the tail and for decode (the reference calls
-    flash-attn here, anchor_attention.py:76-88,101-113).  Returns [B,H,q,D].
-    A library call (torch SDPA), in chunks of DENSE_CHUNK queries so that the mask of a
-    chunked prefill (many queries against a long cache) stays small; a query chunk only
-    sees the keys up to its own last position."""
+    all keys; the path of the tail and of decode (the reference calls flash-attn here,
+    anchor_attention.py:76-88,101-113).  Returns [B,H,q,D].
+    With DENSE_KERNEL_MIN_Q or more queries (the tail of a prefill, a later prefill chunk) on a
+    GPU it runs on the library's own attention kernel (``ops.dense_causal_attention``).  Decode
+    (a few queries) and CPU tensors go to torch SDPA, in chunks of DENSE_CHUNK queries so that the
+    mask stays small; a query chunk only sees the keys up to its own last position."""
     q_len, kv_len = query.shape[2], key.shape[2]
+    if (query.is_cuda and q_len >= DENSE_KERNEL_MIN_Q and query.dtype == torch.bfloat16 and query.shape[3] == 128
+            and q_offset + q_len == kv_len):
+        from .ops import dense_causal_attention
+        return dense_causal_attention(query, key, value, scaling)
     outs = []
     for c0 in range(0, q_len, DENSE_CHUNK):
         c1 = min(q_len, c0 + DENSE_CHUNK)

@@ -325,9 +325,9 @@ def parity_check(call, Q, K, V, full, N, W, rank, q_lo, theta, dev):
             "oracle_s": time.perf_counter() - t0, "ok": bool(ok)}
 
 
-def timed_step3(call, seconds, sampler_index):
-    """Repeats the whole operator for about ``seconds`` with the SM clock sampled, step 3 bracketed by
-    CUDA events.  Returns (mean step-3 ms, median SM MHz)."""
+def timed_steps(call, seconds, sampler_index):
+    """Repeats the whole operator for about ``seconds`` with the SM clock sampled, the three steps
+    bracketed by CUDA events.  Returns ([step-1, step-2, step-3 ms] medians, median SM MHz)."""
     import torch
     for _ in range(3):
         call.run()
@@ -338,23 +338,20 @@ def timed_step3(call, seconds, sampler_index):
     t_end = time.perf_counter() + seconds
     while time.perf_counter() < t_end:
         for _ in range(4):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            call.step1()
-            call.step2()
-            a.record()
-            call.step3()
-            b.record()
-            evs.append((a, b))
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            e[0].record(); call.step1(); e[1].record(); call.step2(); e[2].record(); call.step3(); e[3].record()
+            evs.append(e)
         torch.cuda.synchronize()
     clocks = sampler.stop()
-    return statistics.mean(a.elapsed_time(b) for a, b in evs), clocks.get("sm_mhz")
+    return [statistics.median(e[i].elapsed_time(e[i + 1]) for e in evs) for i in range(3)], clocks.get("sm_mhz")
 
 
 def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
     """Single-GPU extras, outside the headline timing.
     aux_sparse: the labelled AUXILIARY distribution (q_shift 0.5) at 32768 tokens, where the id
-    lists are sparse and step 3 runs through its gather pass: density, step-3 time (gather pass
-    included) and TFLOP/s on the selected pairs for theta 9 and 10.
+    lists are sparse and step 3 runs through its gather pass: density, step times (step 3 with its
+    gather pass) and TFLOP/s on the selected pairs for theta 8, 9 and 10, each from a loop of about
+    one second with the SM clock sampled.
     clock_normalised: step-3 SM cycles per 128-id tile and query-tile pair (launch time x median
     sampled SM clock / tile pairs / 148 SMs) for the benchmark launch and for the dense
     32768-token layer, each from a loop of about two seconds; equal cycles mean the difference in
@@ -367,24 +364,19 @@ def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
     cap = H * sum(b * G - 2 * BLOCK for b in range(1, N_AUX // G))
     aux = {"note": "AUXILIARY distribution, not the benchmark configuration", "seq": N_AUX, "q_shift": 0.5, "cases": []}
     Q, K, V = make_inputs(N_AUX, H, HKV, seed=0, rope=True, device=dev, q_shift=0.5)
-    for theta in (9.0, 10.0):
+    for theta in (8.0, 9.0, 10.0):
         call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, theta)
-        for _ in range(3):
-            call.run()
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(10)]
-        for e in ev:
-            e[0].record(); call.step1(); e[1].record(); call.step2(); e[2].record(); call.step3(); e[3].record()
-        torch.cuda.synchronize()
+        t, mhz = timed_steps(call, 1.0, local)
         call.check_status()
-        t = [statistics.median(e[i].elapsed_time(e[i + 1]) for e in ev) for i in range(3)]
         cnt = int(call.counts.sum())
         aux["cases"].append({"theta": theta, "density": cnt / cap, "step1_ms": t[0], "step2_ms": t[1], "step3_ms": t[2],
-                             "gathered_tiles": call.gather_slots_used,
+                             "sm_mhz": mhz, "gathered_tiles": call.gather_slots_used,
                              "step3_tflops_selected_pairs": 4 * D * G * cnt / (t[2] * 1e-3) / 1e12})
     del Q, K, V
     Q, K, V = make_inputs(N_AUX, H, HKV, seed=0, rope=True, device=dev)
     call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA)
-    ms32, mhz32 = timed_step3(call, 2.0, local)
+    t32, mhz32 = timed_steps(call, 2.0, local)
+    ms32 = t32[2]
     cnt32 = int(call.counts.sum())
 
     def cycles(ms, mhz, cnt):

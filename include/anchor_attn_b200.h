@@ -86,7 +86,11 @@ typedef struct aa_params {
 typedef struct aa_workspace_layout {
     size_t m_off;        /* float   [B,H,N]          row maxima of step 1 (log2 domain)        */
     size_t l_off;        /* float   [B,H,N]          softmax denominators of step 1             */
-    size_t acc_off;      /* float   [B,H,N,D]        un-normalised outputs of step 1            */
+    size_t acc_off;      /* float   [B,H,N/128,D/4,128,4]  un-normalised outputs of step 1, in tiles of
+                                                     128 rows, each tile chunk-major: the 16-byte chunk k
+                                                     (columns 4k..4k+3) of row r is at float offset
+                                                     512 k + 4 r of the tile (steps 1 and 3 touch it with
+                                                     one thread per row; this makes their accesses contiguous) */
     size_t qpool_off;    /* bf16    [B,H,N/bs,D]     block-mean queries                         */
     size_t apool_off;    /* float   [B,H,N/bs]       block-mean anchors (bf16-valued)           */
     size_t bitmap_off;   /* uint32  [B,H,NB,N/32]    hit bitmap of step 2                       */
@@ -297,6 +301,33 @@ int aa_block_sparse_attend(const aa_block_sparse_t *a, void *stream);
 /* Synchronises the stream; AA_OK, AA_ERR_DEVICE_TIMEOUT (a bounded wait gave up) or
  * AA_ERR_UNSORTED (a row of block_index was not ascending; the output is then undefined). */
 int aa_block_sparse_check_status(const aa_block_sparse_t *a, void *stream);
+
+/*
+ * Dense causal attention of the last Nq positions of an Nkv-long sequence: query row i (position
+ * Nkv - Nq + i) attends keys 0 .. Nkv - Nq + i.  The path of the reference's dense calls
+ * (modules/llama/anchor_attention.py:76-88 for the last q_len % (block_size*step) queries of a
+ * prefill, :101-113 for later chunks), which go to flash-attn there.  It is the comparator's
+ * attention kernel with the key-block lists made up on the fly (every block up to the diagonal)
+ * and the causal mask placed by the row's position; softmax state from empty, bf16, D = 128.
+ * q, out: [B, H, Nq, D]; k, v: [B, Hkv, Nkv, D]; strides as in aa_params_t; any Nq >= 1, Nkv >= Nq
+ * (rows are padded to 256 inside the kernel and never written).  `status` is a 16-byte aligned
+ * device array of 4 int32 the call clears; [0] != 0 afterwards means a bounded wait gave up.
+ * One launch.  A 128-row tile per row group makes it a prefill kernel: for single-token decode a
+ * split-KV kernel is the right tool and the host side keeps calling the library one.
+ */
+typedef struct aa_dense_causal {
+    int32_t B, H, Hkv, Nq, Nkv, D;
+    int32_t dtype;                 /* AA_BF16 */
+    double  sm_scale;              /* 0 => D^-0.5 */
+    const void *q, *k, *v;
+    void       *out;
+    int64_t q_stride_b, q_stride_h, q_stride_n;
+    int64_t k_stride_b, k_stride_h, k_stride_n;
+    int64_t v_stride_b, v_stride_h, v_stride_n;
+    int64_t o_stride_b, o_stride_h, o_stride_n;
+    int32_t *status;
+} aa_dense_causal_t;
+int aa_dense_causal_attend(const aa_dense_causal_t *a, void *stream);
 
 const char *aa_strerror(int code);
 /* Text of the last CUDA error this library saw on the calling thread. */

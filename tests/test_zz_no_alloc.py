@@ -58,6 +58,8 @@ def test_static_entry_matches_workspace_entry_on_consecutive_calls(lib):
     for Q, K, M, counts, ids, theta, _, _ in prepared:
         assert _static_call(lib, Q, K, M, counts, ids, theta) == 0
     torch.cuda.synchronize()
+    # none of the bounded device-side waits of these calls gave up (the word lives in the fixed array)
+    assert lib.aa_step2_stripes_static_check_status(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
     for Q, K, M, counts, ids, theta, counts_ref, ids_ref in prepared:
         assert torch.equal(counts, counts_ref)          # integer work: bit-exact
         assert int(counts.sum()) > 0 or theta < 5
