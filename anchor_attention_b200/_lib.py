@@ -19,7 +19,7 @@ EXPORTS = [
     "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
     "aa_selftest_wait_timeout", "aa_block_sparse_workspace_bytes", "aa_block_sparse_attend",
     "aa_block_sparse_check_status", "aa_validate_lists", "aa_step2_stripes_static_check_status",
-    "aa_peer_barrier", "aa_dense_causal_attend",
+    "aa_peer_barrier", "aa_dense_causal_attend", "aa_rope_dispatch",
 ]
 MAX_PEERS = 8
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -94,6 +94,17 @@ class AADenseCausal(ctypes.Structure):
     ]
 
 
+class AARopeDispatch(ctypes.Structure):
+    _fields_ = [
+        ("n", ctypes.c_int32), ("H", ctypes.c_int32), ("Hkv", ctypes.c_int32), ("D", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("n_peers", ctypes.c_int32), ("token0", ctypes.c_int32),
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("q_stride_n", ctypes.c_int64), ("k_stride_n", ctypes.c_int64), ("v_stride_n", ctypes.c_int64),
+        ("cos", ctypes.c_void_p), ("sin", ctypes.c_void_p),
+        ("dst", ctypes.c_void_p * MAX_PEERS),
+    ]
+
+
 class AAPeerBarrier(ctypes.Structure):
     _fields_ = [("n_peers", ctypes.c_int32), ("rank", ctypes.c_int32), ("epoch", ctypes.c_int32),
                 ("timeout_ms", ctypes.c_uint32), ("flags", ctypes.c_void_p * MAX_PEERS), ("status", ctypes.c_void_p)]
@@ -129,6 +140,8 @@ def load():
     lib.aa_step3_sparse_push.restype = ctypes.c_int
     lib.aa_dense_causal_attend.argtypes = [ctypes.POINTER(AADenseCausal), ctypes.c_void_p]
     lib.aa_dense_causal_attend.restype = ctypes.c_int
+    lib.aa_rope_dispatch.argtypes = [ctypes.POINTER(AARopeDispatch), ctypes.c_void_p]
+    lib.aa_rope_dispatch.restype = ctypes.c_int
     lib.aa_peer_barrier.argtypes = [ctypes.POINTER(AAPeerBarrier), ctypes.c_void_p]
     lib.aa_peer_barrier.restype = ctypes.c_int
     PB = ctypes.POINTER(AABlockSparse)

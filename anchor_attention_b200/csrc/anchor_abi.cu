@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "gather.cuh"
 #include "peer_barrier.cuh"
+#include "rope_dispatch.cuh"
 #include "score_tc.cuh"
 #include "stripe.cuh"
 
@@ -520,6 +521,36 @@ int aa_peer_barrier(const aa_peer_barrier_t* b, void* stream) {
     aa::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? AA_OK : cuda_fail(e, "launch peer barrier");
+}
+
+int aa_rope_dispatch(const aa_rope_dispatch_t* r, void* stream) {
+    if (!r) return AA_ERR_NULL;
+    if (r->n <= 0 || r->H <= 0 || r->Hkv <= 0 || r->n_peers < 1 || r->n_peers > AA_MAX_PEERS || r->token0 < 0 ||
+        r->H % r->n_peers != 0 || r->Hkv % r->n_peers != 0)
+        return AA_ERR_SHAPE;
+    if (r->D != 128) return AA_ERR_HEAD_DIM;
+    if (r->dtype != AA_BF16) return AA_ERR_DTYPE;
+    if (!r->q || !r->k || !r->v || !r->cos || !r->sin) return AA_ERR_NULL;
+    if (!stride_ok(r->q_stride_n) || !stride_ok(r->k_stride_n) || !stride_ok(r->v_stride_n)) return AA_ERR_STRIDE;
+    if (((uintptr_t)r->q | (uintptr_t)r->k | (uintptr_t)r->v | (uintptr_t)r->cos | (uintptr_t)r->sin) & 15)
+        return AA_ERR_STRIDE;
+    aa::RopeDispatchArgs a;
+    for (int i = 0; i < aa::kRopeMaxPeers; ++i) a.dst[i] = nullptr;
+    for (int i = 0; i < r->n_peers; ++i) {
+        if (!r->dst[i]) return AA_ERR_NULL;
+        if ((uintptr_t)r->dst[i] & 15) return AA_ERR_STRIDE;
+        a.dst[i] = static_cast<__nv_bfloat16*>(r->dst[i]);
+    }
+    a.q = static_cast<const __nv_bfloat16*>(r->q);
+    a.k = static_cast<const __nv_bfloat16*>(r->k);
+    a.v = static_cast<const __nv_bfloat16*>(r->v);
+    a.q_sn = r->q_stride_n; a.k_sn = r->k_stride_n; a.v_sn = r->v_stride_n;
+    a.cos = static_cast<const __nv_bfloat16*>(r->cos);
+    a.sin = static_cast<const __nv_bfloat16*>(r->sin);
+    a.n = r->n; a.H = r->H; a.Hkv = r->Hkv; a.n_peers = r->n_peers; a.token0 = r->token0;
+    aa::rope_dispatch_kernel<<<(r->n + 15) / 16, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AA_OK : cuda_fail(e, "launch rope dispatch");
 }
 
 int aa_forward(const aa_params_t* p, void* stream) {

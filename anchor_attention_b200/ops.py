@@ -20,8 +20,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_host", "AnchorAttnCall",
-           "dense_causal_attention", "launches_per_forward"]
+__all__ = ["anchor_attn", "anchor_attn_without_anchor", "anchor_attn_test_time", "anchor_attn_host",
+           "AnchorAttnCall", "dense_causal_attention", "launches_per_forward"]
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 _NVTX = os.environ.get("ANCHOR_ATTN_NVTX", "0") == "1"
@@ -265,6 +265,33 @@ def anchor_attn_without_anchor(Q, K, V,
     171-224): the same three steps with the same arithmetic as ``anchor_attn``; it always
     returns ``(out, sparsity_ratio)``."""
     return anchor_attn(Q, K, V, sm_scale, block_size, step, difference, return_computational_ratio=True)
+
+
+def anchor_attn_test_time(Q, K, V,
+                          sm_scale: float = None,
+                          block_size: int = 128,
+                          step: int = 16,
+                          difference: float = 12,
+                          return_computational_ratio: bool = True):
+    """The reference's timing entry point (anchor_attn/src/ops/anchor_attn_v4.py:328-354, 107-169):
+    the same operator with the host synchronised around the search phase (steps 1 and 2) and the
+    compute phase (step 3), wall-clock milliseconds of each returned after the output.  Returns
+    ``(out, ratio, search_ms, compute_ms)`` or ``(out, search_ms, compute_ms)``."""
+    import time
+    call = AnchorAttnCall(Q, K, V, sm_scale, block_size, step, difference)
+    torch.cuda.synchronize(Q.device)
+    t0 = time.time()
+    call.step1()
+    call.step2()
+    torch.cuda.synchronize(Q.device)
+    search_ms = (time.time() - t0) * 1000
+    t0 = time.time()
+    out = call.step3()
+    torch.cuda.synchronize(Q.device)
+    compute_ms = (time.time() - t0) * 1000
+    if return_computational_ratio:
+        return out, call.ratio(), search_ms, compute_ms
+    return out, search_ms, compute_ms
 
 
 def anchor_attn_host(Q, K, V, out=None,

@@ -11,9 +11,13 @@ independent per query head.  So rank r of W
 
 Two exchanges per layer turn one partition into the other:
 
-  tokens -> heads   the rotated q/k/v of a rank's tokens go to the ranks that own the heads:
-                    one all-to-all (each rank receives N x (h + 2 hkv) x D elements, token-major,
-                    which the attention kernels read in place through their strides);
+  tokens -> heads   the rotated q/k/v of a rank's tokens go to the ranks that own the heads
+                    (each rank receives N x (h + 2 hkv) x D elements, token-major, which the
+                    attention kernels read in place through their strides): one kernel
+                    (``aa_rope_dispatch``) applies the rotary embedding and stores every head row
+                    straight into its owner's buffer over NVLink, then the flag barrier; or, with
+                    ``exchange="all_to_all"``, the library rotary function, a packing copy and one
+                    all-to-all collective;
   heads -> tokens   step 3 stores every finished output row straight into the [n_loc, H, D]
                     buffer of the rank that owns the row's token (``aa_step3_sparse_push`` with
                     ``rows_per_peer``: plain stores over NVLink while the other CTAs compute),
@@ -59,6 +63,7 @@ class SequenceParallelPrefill:
         self.block, self.step, self.theta = int(cfg.block_size_M), int(cfg.step), float(cfg.theta)
         self.q_lo, self.q_hi, self.kv_lo, self.kv_hi = head_partition(self.H, self.Hkv, self.W, self.rank)
         self._pushed = None
+        self._qkv = None
         self.last_call = None
         self.profile = False          # True: the next call records CUDA events between the stages of every layer
         self.stage_ms = {}            # stage -> milliseconds summed over the layers of the last profiled call
@@ -83,6 +88,38 @@ class SequenceParallelPrefill:
         Q = recv[:, :, :h].permute(0, 2, 1, 3)
         K = recv[:, :, h:h + hkv].permute(0, 2, 1, 3)
         V = recv[:, :, h + hkv:].permute(0, 2, 1, 3)
+        return Q, K, V
+
+    def _rope_dispatch(self, qp, kp, vp, cos, sin, lo):
+        """The fused path of the tokens -> heads exchange: qp [1,n,H*D], kp/vp [1,n,Hkv*D] are the
+        projections of this rank's tokens, cos/sin [1,n,D] their rotary tables; returns (Q, K, V) of
+        this rank's heads over all tokens as strided views of its symmetric buffer."""
+        import ctypes
+        from . import _lib
+        W, n = self.W, qp.shape[1]
+        h, hkv, D = self.H // W, self.Hkv // W, self.D
+        N = W * n
+        if self._qkv is None or self._qkv.shape != (1, N, h + 2 * hkv, D):
+            self._qkv = PushedOutput(1, N, h + 2 * hkv, D, qp.dtype, qp.device, self.group, self.timeout_ms)
+        buf, ptrs = self._qkv.next()
+        r = _lib.AARopeDispatch()
+        r.n, r.H, r.Hkv, r.D, r.dtype = n, self.H, self.Hkv, D, _lib.AA_BF16
+        r.n_peers, r.token0 = W, lo
+        r.q, r.k, r.v = qp.data_ptr(), kp.data_ptr(), vp.data_ptr()
+        r.q_stride_n, r.k_stride_n, r.v_stride_n = qp.stride(1), kp.stride(1), vp.stride(1)
+        cos, sin = cos.contiguous(), sin.contiguous()
+        r.cos, r.sin = cos.data_ptr(), sin.data_ptr()
+        for i, p in enumerate(ptrs):
+            r.dst[i] = p
+        with torch.cuda.device(qp.device):
+            rc = _lib.load().aa_rope_dispatch(ctypes.byref(r),
+                                              ctypes.c_void_p(torch.cuda.current_stream(qp.device).cuda_stream))
+        if rc != _lib.AA_OK:
+            raise RuntimeError(f"aa_rope_dispatch: {_lib.error_text(rc)}")
+        self._qkv.barrier()
+        Q = buf[:, :, :h].permute(0, 2, 1, 3)
+        K = buf[:, :, h:h + hkv].permute(0, 2, 1, 3)
+        V = buf[:, :, h + hkv:].permute(0, 2, 1, 3)
         return Q, K, V
 
     def _heads_to_tokens(self, out_heads):
@@ -140,18 +177,25 @@ class SequenceParallelPrefill:
         pos = torch.arange(lo, lo + n, device=x.device)[None]
         cos, sin = base.rotary_emb(x, position_ids=pos)
         H, Hkv, D = self.H, self.Hkv, self.D
+        fused = (self.attn_fn is None and self.exchange == "push" and x.is_cuda and x.dtype == torch.bfloat16
+                 and D == 128)
         marks = [] if (self.profile and x.is_cuda) else None
         self._mark(marks, "start")
         for layer in base.layers[: model.config.num_hidden_layers]:
             attn = layer.self_attn
             hn = layer.input_layernorm(x)
-            q = attn.q_proj(hn).view(1, n, H, D).transpose(1, 2)
-            k = attn.k_proj(hn).view(1, n, Hkv, D).transpose(1, 2)
-            v = attn.v_proj(hn).view(1, n, Hkv, D)
-            q, k = apply_rotary_pos_emb(q, k, cos, sin)
-            self._mark(marks, "norm_qkv_rope")
-            Q, K, V = self._tokens_to_heads(q.transpose(1, 2), k.transpose(1, 2), v)
-            self._mark(marks, "tokens_to_heads")
+            qp, kp, vp = attn.q_proj(hn), attn.k_proj(hn), attn.v_proj(hn)
+            if fused:
+                self._mark(marks, "norm_qkv")
+                Q, K, V = self._rope_dispatch(qp, kp, vp, cos, sin, lo)
+                self._mark(marks, "rope_and_tokens_to_heads")
+            else:
+                q = qp.view(1, n, H, D).transpose(1, 2)
+                k = kp.view(1, n, Hkv, D).transpose(1, 2)
+                q, k = apply_rotary_pos_emb(q, k, cos, sin)
+                self._mark(marks, "norm_qkv_rope")
+                Q, K, V = self._tokens_to_heads(q.transpose(1, 2), k.transpose(1, 2), vp.view(1, n, Hkv, D))
+                self._mark(marks, "tokens_to_heads")
             out = self._attention(Q, K, V, attn.scaling, n)                 # [1, n, H, D]
             self._mark(marks, "attention_and_heads_to_tokens")
             x = x + attn.o_proj(out.reshape(1, n, H * D))
@@ -177,3 +221,5 @@ class SequenceParallelPrefill:
             self.last_call.check_status()
         if self._pushed is not None:
             self._pushed.check_status()
+        if self._qkv is not None:
+            self._qkv.check_status()

@@ -192,6 +192,26 @@ typedef struct aa_peer_barrier {
 } aa_peer_barrier_t;
 int aa_peer_barrier(const aa_peer_barrier_t *b, void *stream);
 
+/* Tokens -> heads exchange of a sequence-parallel prefill, fused with the rotary embedding: reads
+ * the q/k/v projections of this rank's n tokens (q [n,H,128], k/v [n,Hkv,128] bf16, row strides
+ * in elements, heads 128 apart), rotates q and k with the rotate-half formulation on bf16 values,
+ * rounding included (what apply_rotary_pos_emb computes in the reference's forward,
+ * modules/llama/anchor_attention.py:38-48; cos/sin are [n,128] bf16), and stores every head row
+ * into dst[d] of the rank d that owns the head: a [N, h + 2*hkv, 128] token-major buffer
+ * (h = H / n_peers query heads, then hkv = Hkv / n_peers key heads, then the value heads), at
+ * token row token0 + i.  Plain coalesced stores, to peer memory for d != this rank; replaces the
+ * rotary kernels, the packing copies (anchor_attention.py:89-91) and an all-to-all.  Follow it
+ * with aa_peer_barrier before any rank reads its buffer.  One launch, no synchronisation. */
+typedef struct aa_rope_dispatch {
+    int32_t n, H, Hkv, D, dtype;
+    int32_t n_peers, token0;
+    const void *q, *k, *v;
+    int64_t q_stride_n, k_stride_n, v_stride_n;
+    const void *cos, *sin;
+    void   *dst[AA_MAX_PEERS];
+} aa_rope_dispatch_t;
+int aa_rope_dispatch(const aa_rope_dispatch_t *r, void *stream);
+
 /* Reads the device status words (synchronises the stream first).  Returns AA_OK,
  * AA_ERR_DEVICE_TIMEOUT, AA_ERR_BAD_LIST or AA_ERR_CUDA. */
 int aa_check_status(const aa_params_t *p, void *stream);

@@ -149,6 +149,7 @@ def test_ctypes_mirrors_match_the_header(tmp_path):
         "aa_push_t": (_lib.AAPush, ["n_peers", "rows_per_peer", "out"]),
         "aa_peer_barrier_t": (_lib.AAPeerBarrier, ["n_peers", "epoch", "timeout_ms", "flags", "status"]),
         "aa_dense_causal_t": (_lib.AADenseCausal, ["B", "Nkv", "dtype", "sm_scale", "q", "o_stride_n", "status"]),
+        "aa_rope_dispatch_t": (_lib.AARopeDispatch, ["n", "dtype", "token0", "q", "v_stride_n", "cos", "dst"]),
         "aa_block_sparse_t": (_lib.AABlockSparse, ["B", "max_blocks", "sm_scale", "q", "o_stride_n", "block_index",
                                                    "workspace_bytes"]),
     }

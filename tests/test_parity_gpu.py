@@ -177,6 +177,18 @@ def test_strided_layouts_and_expanded_kv(lib):
     assert torch.equal(anchor_attn(Qc, Ke, Ve, difference=9.5, return_computational_ratio=False), base)
 
 
+def test_timing_entry_point_mirrors_the_reference(lib):
+    """anchor_attn_test_time: same output as anchor_attn, plus the two phase times."""
+    from anchor_attention_b200 import anchor_attn, anchor_attn_test_time
+    Q, K, V = (t.cuda() for t in make_inputs(4096, 2, 1, seed=3, rope=True, q_shift=0.5))
+    out, ratio, search_ms, compute_ms = anchor_attn_test_time(Q, K, V, difference=10)
+    want, want_ratio = anchor_attn(Q, K, V, difference=10)
+    assert torch.equal(out, want) and float(ratio) == float(want_ratio)
+    assert search_ms > 0 and compute_ms > 0
+    out2, s2, c2 = anchor_attn_test_time(Q, K, V, difference=10, return_computational_ratio=False)
+    assert torch.equal(out2, want)
+
+
 def test_reference_layout_export(lib):
     N, H = 6144, 2
     Q, K, V = make_inputs(N, H, 1, seed=2, rope=True, q_shift=0.5)
