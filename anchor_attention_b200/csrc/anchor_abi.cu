@@ -230,7 +230,6 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     ta.status = ws_ptr<int32_t>(p, lay.status_off);
     ta.n_peers = 0;
     ta.rows_per_peer = 0;
-    ta.wave = 0;
     ta.dense = 0;
     ta.q_rows = p->N;
     ta.q_off = 0;
@@ -241,13 +240,6 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
         ta.q_rows = dense->q_rows;
         ta.q_off = dense->kv_rows - dense->q_rows;
         ta.kv_blocks = (dense->kv_rows + aa::tc::kTile - 1) / aa::tc::kTile;
-    }
-    if (MODE != aa::kBlock) {
-        static thread_local int sm_count[64] = {};
-        if (dev >= 0 && dev < 64) {
-            if (!sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-            ta.wave = sm_count[dev];
-        }
     }
     ta.tile_slot = nullptr;
     ta.gather = nullptr;

@@ -80,7 +80,6 @@ struct TcArgs {
     const int32_t* tile_slot;        // step 3 only: gather slot of every id tile ([B*H, ids_per_head/128]) or NULL
     const uint8_t* gather;           // step 3 only: the 64 KB slots (K image, V image) the gather pass filled
     int n_slots;                     // step 3 only: slots in `gather`; a table entry beyond it is ignored
-    int wave;                        // CTAs resident at a time (one per SM): CTA i + wave starts about when CTA i ends
     int n_peers;                     // step 3 only: > 0 -> write the output to peers[0 .. n_peers) instead of a.out
     int rows_per_peer;               // with n_peers > 0: 0 -> every row goes to every peer; > 0 -> row n goes only to
                                      // peer n / rows_per_peer, at row n % rows_per_peer of that peer's buffer
@@ -463,29 +462,6 @@ __device__ __forceinline__ WorkItem work_item(const AttendArgs& a, int bid) {
     return w;
 }
 
-// A CTA reads 256 query rows (64 KB) and, in step 3, their step-1 state M, L (2 KB) and Acc
-// (128 KB) before it can do anything; with short id lists that is most of a CTA's life.  These ranges are
-// asked into L2 ahead of time with bulk prefetches issued by one warp (`lane` of it): by the CTA
-// itself as its first action, and by the CTA that runs one wave earlier once its own loads are
-// issued, so that the fetches overlap that CTA's arithmetic and output.
-__device__ __forceinline__ void prefetch_inputs(const AttendArgs& a, const WorkItem& w, int lane, bool with_state) {
-    const int64_t srow0 = (int64_t)w.hz * a.N + (int64_t)w.pair * 2 * kTile;
-    if (!with_state) {
-        // step 1 starts from an empty state: only the query rows
-    } else if (lane < 4) {
-        // the state of the pair's two tiles is contiguous: 4 x 32 KB
-        bulk_prefetch_l2(reinterpret_cast<const char*>(a.Acc + srow0 * kD) + lane * 32768, 32768);
-    } else if (lane < 6) {
-        bulk_prefetch_l2((lane == 4 ? a.M : a.L) + srow0, 2 * kTile * 4);
-    }
-    const __nv_bfloat16* q = a.q.ptr + w.z * a.q.sb + w.h * a.q.sh + (int64_t)w.pair * 2 * kTile * a.q.sn;
-    if (a.q.sn == kD) {
-        if (lane >= 6 && lane < 8) bulk_prefetch_l2(q + (lane - 6) * kTile * kD, kTileBytes);
-    } else {
-        for (int r = lane; r < 2 * kTile; r += 32) bulk_prefetch_l2(q + (int64_t)r * a.q.sn, kRowBytes);
-    }
-}
-
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -514,7 +490,6 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
     const int npairs = a.N / (2 * kTile);
     const WorkItem wi = work_item(a, (int)blockIdx.x);
     const int pair = wi.pair, z = wi.z, kvh = wi.kvh, h = wi.h, hz = wi.hz;
-    const bool has_next = MODE != kBlock && ta.wave > 0 && blockIdx.x + (unsigned)ta.wave < gridDim.x;
     const int G = a.block * a.step;
     const int b = (pair * 2 * kTile) / G;
     const int NB = a.N / G;
@@ -543,7 +518,6 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         const int64_t row_off = (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)a.block * (b - 1));
         idp = a.ids + (int64_t)hz * a.ids_per_head + row_off;
         if (ta.tile_slot) slotp = ta.tile_slot + (int64_t)hz * (a.ids_per_head / kTile) + row_off / kTile;
-        if (warp == 0) prefetch_inputs(a, wi, lane, true);        // this CTA's own inputs, in case nobody asked before
     }
 
     if (MODE == kStripe && ntiles == 0) {
@@ -554,7 +528,6 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
         // and the warp turns its 32 x 64 bytes of bf16 through shared memory so that the rows go
         // out as 64-byte pieces from four consecutive lanes.
         constexpr int kWarps = kThreads / 32;
-        if (has_next && warp == kWarps - 1) prefetch_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), lane, true);
         uint8_t* wbuf = smem + warp * 2048;
         for (int u = warp; u < 32; u += kWarps) {
             const int row = (u >> 2) * 32 + lane, quarter = u & 3;          // row inside the pair's 256 rows
@@ -870,9 +843,6 @@ attend_tc_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant
                     cp_async_mbar_arrive_noinc(kv_full(slot));
                 }
             }
-            // every load of this CTA is under way: ask for the inputs of the CTA one wave later
-            if (has_next && lw == kLoaderWarps - 1)
-                prefetch_inputs(a, work_item(a, (int)blockIdx.x + ta.wave), lane, MODE == kStripe);
             cp_async_wait<0>();
         }
     }

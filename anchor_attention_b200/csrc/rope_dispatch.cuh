@@ -53,9 +53,10 @@ __global__ void __launch_bounds__(256) rope_dispatch_kernel(RopeDispatchArgs a) 
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out_hi);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            // each bf16 product and sum is rounded once (packed bf16 arithmetic does exactly that)
-            ol[e] = __hadd2(__hmul2(l2[e], cl[e]), __hmul2(__hneg2(h2[e]), sl[e]));
-            oh[e] = __hadd2(__hmul2(h2[e], ch[e]), __hmul2(l2[e], sh[e]));
+            // each bf16 product and sum is rounded on its own: the _rn forms are never contracted
+            // into a fused multiply-add, which would skip the rounding of the product
+            ol[e] = __hadd2_rn(__hmul2_rn(l2[e], cl[e]), __hmul2_rn(__hneg2(h2[e]), sl[e]));
+            oh[e] = __hadd2_rn(__hmul2_rn(h2[e], ch[e]), __hmul2_rn(l2[e], sh[e]));
         }
     };
     const int64_t drow = (int64_t)(a.token0 + tok) * width * kD;

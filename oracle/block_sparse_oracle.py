@@ -71,6 +71,48 @@ def block_sparse_attention_oracle(q, k, v, block_index, sm_scale=None, mode="bf1
     return out
 
 
+def dense_causal_tail_oracle(q, k, v, sm_scale=None, mode="bf16") -> torch.Tensor:
+    """Dense causal attention of the LAST Nq positions of an Nkv-long sequence with the arithmetic
+    of the block kernel above: q [B,H,Nq,D], k/v [B,Hkv,Nkv,D]; row i sits at position
+    Nkv - Nq + i and attends keys 0 .. Nkv - Nq + i.  The semantics of the reference's dense calls
+    for the prefill tail and later chunks (anchor_attn/src/modules/llama/anchor_attention.py:76-88,
+    101-113, which go to flash-attn with causal=True, bottom-right aligned; flash-attn's own
+    arithmetic is not pinned by anything in the reference).  Rounding points as in the block
+    kernel: scaled queries and probabilities rounded to the input type, everything else fp32;
+    128-row query tiles counted from the first tail row, 128-key blocks in ascending order."""
+    rd = _rounder(mode)
+    B, H, Nq, D = q.shape
+    Hkv, Nkv = k.shape[1], k.shape[2]
+    off = Nkv - Nq
+    sm = (D ** -0.5) if sm_scale is None else sm_scale
+    qk_scale = f32(f32(sm) * f32(LOG2E))
+    out = torch.empty(B, H, Nq, D, dtype=torch.float32)
+    for b in range(B):
+        for h in range(H):
+            kf = k[b, h // (H // Hkv)].to(torch.float32)
+            vf = v[b, h // (H // Hkv)].to(torch.float32)
+            qs = rd(q[b, h].to(torch.float32) * qk_scale)
+            for r0 in range(0, Nq, BLOCK):
+                r1 = min(Nq, r0 + BLOCK)
+                pos = off + torch.arange(r0, r1)
+                m_i = torch.full((r1 - r0,), -float("inf"))
+                l_i = torch.zeros(r1 - r0)
+                acc = torch.zeros(r1 - r0, D)
+                for c0 in range(0, int(pos[-1]) + 1, BLOCK):
+                    c1 = min(Nkv, c0 + BLOCK)
+                    cols = torch.arange(c0, c1)
+                    s = qs[r0:r1] @ kf[c0:c1].T
+                    s = torch.where(cols[None, :] <= pos[:, None], s, torch.full_like(s, -float("inf")))
+                    m_new = torch.maximum(m_i, s.max(dim=1).values)
+                    alpha = torch.exp2(m_i - m_new)
+                    p = torch.exp2(s - m_new[:, None])
+                    acc = acc * alpha[:, None] + rd(p) @ vf[c0:c1]
+                    l_i = l_i * alpha + p.sum(dim=1)
+                    m_i = m_new
+                out[b, h, r0:r1] = rd(acc / l_i[:, None])
+    return out
+
+
 def _pooled_scores(query, key, scale):
     """Block means (in the input dtype, as ``Tensor.mean`` gives them), optional scale, scores
     of block means, -inf above the diagonal (:166-174)."""

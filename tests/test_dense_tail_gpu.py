@@ -1,12 +1,14 @@
 """Dense causal attention of the last q positions over kv keys on the library's own kernel
-(the tail of a prefill, a later prefill chunk), through the C ABI, against fp32 dense softmax.
+(the tail of a prefill, a later prefill chunk), through the C ABI.
 
-Tolerance: both sides see bf16 inputs; the kernel rounds the scaled queries and the
-probabilities to bf16 as the sparse operator does, so 2e-2 max / 1e-3 mean as there."""
+Checked against the CPU restatement with the kernel's rounding points (scaled queries and
+probabilities rounded to bf16): max 2e-2 / mean 1e-3, the operator's tolerance; and against exact
+fp32 dense softmax on the same bf16 inputs, where those two roundings show: max 5e-2 / mean 3e-3."""
 import pytest
 import torch
 
 from oracle.anchor_oracle import dense_causal_attention as dense_oracle, make_inputs
+from oracle.block_sparse_oracle import dense_causal_tail_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -24,11 +26,13 @@ def test_dense_tail_matches_dense_softmax(lib, nq, nkv, H, Hkv):
     n = ((nkv + 127) // 128) * 128
     Q, K, V = make_inputs(max(n, 2048), H, Hkv, seed=nq, rope=True)
     Q, K, V = Q[:, :, nkv - nq:nkv], K[:, :, :nkv], V[:, :, :nkv]
-    want = dense_oracle(torch.cat([torch.zeros(1, H, nkv - nq, 128, dtype=Q.dtype), Q], dim=2), K, V)[:, :, nkv - nq:]
     got = dense_causal_attention(Q.cuda().contiguous(), K.cuda().contiguous(), V.cuda().contiguous())
-    err = (got.float().cpu() - want).abs()
     assert got.shape == (1, H, nq, 128)
+    err = (got.float().cpu() - dense_causal_tail_oracle(Q, K, V)).abs()
     assert err.max() <= 2e-2 and err.mean() <= 1e-3, (float(err.max()), float(err.mean()))
+    exact = dense_oracle(torch.cat([torch.zeros(1, H, nkv - nq, 128, dtype=Q.dtype), Q], dim=2), K, V)[:, :, nkv - nq:]
+    err = (got.float().cpu() - exact).abs()
+    assert err.max() <= 5e-2 and err.mean() <= 3e-3, (float(err.max()), float(err.mean()))
 
 
 def test_dense_tail_strided_views_and_token_major_output(lib):
