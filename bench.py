@@ -45,10 +45,10 @@ sys.path.insert(0, ROOT)
 H, HKV, D, BLOCK, STEP, THETA = 32, 8, 128, 128, 16, 12.0
 METRIC = "ms_per_layer_anchor_attn_prefill_128k_llama31_8b_heads"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one step-3 launch at density 1 on one
-# GPU, from single-pass ncu captures of this benchmark (profiles/attend_tc_seq32768.md): sequence
+# GPU, from single-pass ncu captures of this benchmark (profiles/launch_list_seq131072.md): sequence
 # length -> (bytes, K/V tile-pair loads of 64 KB by all CTAs).  Other sizes, densities and per-rank
 # shares are scaled from the nearest entry by their tile-pair loads.
-STEP3_DRAM_CAPTURES = {32768: (1.245e9, 483840), 131072: (7.97e9, 8225280)}
+STEP3_DRAM_CAPTURES = {32768: (1.247e9, 483840), 131072: (8.13e9, 8225280)}
 
 
 def algorithmic_flops(N, H, counts_total, step=STEP):
