@@ -6,7 +6,8 @@
 //
 //   kWindow  (step 1)  contiguous tiles of [0, min(G, end)) U [max(b*G, that), end),
 //            end = last query row + 1; additive -1e6 causal mask on diagonal tiles;
-//            query scaled with dtype-rounded constants; writes M, L, Acc.
+//            query scaled with dtype-rounded constants; writes M, L, Acc (Acc in 128-row
+//            chunk-major tiles, see acc_tile()).
 //            Reference: anchor_attn/src/ops/anchor_step_1_2_v2.py:8-161.
 //   kStripe  (step 3)  tiles of 128 ids from the big block's id list; state starts
 //            from step 1's (M, L, Acc); slots past the count masked to -inf;
@@ -16,16 +17,21 @@
 //            other one gets no products for it); -inf causal mask on a tile's own block;
 //            state starts empty; writes bf16(acc / l).
 //            Reference: anchor_attn/src/ops/block_sparse_flash_attention_v2.py:10-110.
+//            Its dense causal variant (the last q rows of a longer sequence attend every key up
+//            to their own position; lists made up on the fly, mask placed by position) serves
+//            the tail of a prefill and later prefill chunks
+//            (anchor_attn/src/modules/llama/anchor_attention.py:76-88, 101-113).
 //
 // Warp roles (384 threads):
 //   warps 0-3   softmax of tile A: thread r owns query row r = tensor-memory lane r
 //   warps 4-7   softmax of tile B
 //   warp  8     MMA issuer (one elected lane): S = Q K^T and O += P V with tcgen05.mma
-//   warps 9-11  loaders: one TMA box load for a run of 128 consecutive rows; discrete
-//               rows are split between TMA row gathers (tile::gather4, four rows per
-//               instruction, warp 9) and 16-byte cp.async copies (warps 10-11; all
-//               three warps for stride patterns no 2-D tensor map covers); into a
-//               5-slot ring of 32 KB tiles
+//   warps 9-11  loaders, into a 5-slot ring of 32 KB tiles: one TMA box load for a run of 128
+//               consecutive rows; one bulk copy for a tile the gather pass (gather.cuh) put
+//               into scratch; discrete rows without a scratch slot are split between TMA row
+//               gathers (tile::gather4, four rows per instruction, warp 9) and 16-byte
+//               cp.async copies (warps 10-11; all three warps for stride patterns no 2-D
+//               tensor map covers)
 //
 // Tensor memory (512 columns): S_A | S_B | O_A | O_B, 128 fp32 columns each.  P (bf16)
 // overwrites the first 64 columns of its S and is consumed from tensor memory as
