@@ -97,6 +97,14 @@ def test_host_buffer_entry_point_matches_device_call(lib):
     want = anchor_attn(Q.cuda(), K.cuda(), V.cuda(), difference=10.0, return_computational_ratio=False).cpu()
     got = anchor_attn_host(Q.pin_memory(), K.pin_memory(), V.pin_memory(), None, None, 128, 16, 10.0)
     assert got.shape == want.shape and torch.equal(got, want)
+    # the head-parallel wrapper's host path (here one rank): query heads streamed one by one
+    from anchor_attention_b200.parallel import HeadShardedAnchorAttn
+    op = HeadShardedAnchorAttn(difference=10.0)
+    out = torch.empty((1, 6, 6144, 128), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        full = op.host_call(Q.pin_memory(), K.pin_memory(), V.pin_memory(), out)
+    op.check_status()
+    assert torch.equal(out, want) and torch.equal(full.cpu().transpose(1, 2), want)
 
 
 def test_operator_replays_from_a_cuda_graph(lib):
