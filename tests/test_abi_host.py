@@ -212,3 +212,52 @@ def test_block_sparse_python_entry_refuses_cpu_tensors():
     idx = torch.zeros(1, 1, 2, 1, dtype=torch.int32)
     with pytest.raises(AssertionError, match="CUDA"):
         block_sparse_attend(q, q, q, idx)
+
+
+def test_new_entry_points_validate_before_touching_cuda(lib):
+    """The barrier, the rotary dispatch, the dense causal variant and the list validator refuse
+    bad arguments on the host, before any CUDA call."""
+    assert lib.aa_peer_barrier(None, None) == -1
+    b = _lib.AAPeerBarrier()
+    b.n_peers, b.rank = 2, 0
+    assert lib.aa_peer_barrier(ctypes.byref(b), None) == -1            # no status word
+    b.status = 4096
+    b.n_peers = _lib.MAX_PEERS + 1
+    assert lib.aa_peer_barrier(ctypes.byref(b), None) == -2
+    b.n_peers, b.rank = 2, 5
+    assert lib.aa_peer_barrier(ctypes.byref(b), None) == -2
+    b.rank = 1
+    assert lib.aa_peer_barrier(ctypes.byref(b), None) == -1            # NULL flag arrays
+
+    assert lib.aa_rope_dispatch(None, None) == -1
+    r = _lib.AARopeDispatch()
+    r.n, r.H, r.Hkv, r.D, r.n_peers = 16, 8, 4, 128, 3                 # 3 ranks do not divide the heads
+    assert lib.aa_rope_dispatch(ctypes.byref(r), None) == -2
+    r.n_peers, r.D = 2, 64
+    assert lib.aa_rope_dispatch(ctypes.byref(r), None) == -3
+    r.D = 128
+    assert lib.aa_rope_dispatch(ctypes.byref(r), None) == -1           # NULL tensors
+
+    assert lib.aa_dense_causal_attend(None, None) == -1
+    d = _lib.AADenseCausal()
+    d.B, d.H, d.Hkv, d.Nq, d.Nkv, d.D = 1, 4, 2, 300, 200, 128         # more queries than keys
+    assert lib.aa_dense_causal_attend(ctypes.byref(d), None) == -2
+    d.Nkv, d.D = 4000, 64
+    assert lib.aa_dense_causal_attend(ctypes.byref(d), None) == -3
+    d.D = 128
+    assert lib.aa_dense_causal_attend(ctypes.byref(d), None) == -1     # NULL tensors / status
+
+    assert lib.aa_validate_lists(None, None) == -1
+    assert lib.aa_validate_lists(ctypes.byref(_params()), None) == -1  # NULL q/k/v/out
+    assert b"malformed" in lib.aa_strerror(-14)
+
+    push = _lib.AAPush()
+    p = _params()
+    p.q = p.k = p.v = p.out = 4096
+    for name in ("q", "k", "v", "o"):
+        setattr(p, f"{name}_stride_n", 128)
+    push.n_peers, push.rows_per_peer = 2, 100                           # not a multiple of the tile height
+    push.out[0] = push.out[1] = 4096
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
+    push.rows_per_peer = 2048                                           # 2 x 2048 rows do not cover N = 8192
+    assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
