@@ -1,11 +1,13 @@
 """Head-parallel execution: the query heads are partitioned by KV-head group
-across the ranks of one node and the head outputs are exchanged with a single
-all-gather (NCCL on GPUs; gloo works for the host-side logic on CPU ranks).
+across the ranks of one node.  The head outputs reach every rank either because
+step 3 stores its rows into every rank's copy of the assembled output over NVLink
+while it computes (a bounded flag barrier follows), or through a single all-gather
+(NCCL on GPUs; gloo works for the host-side logic on CPU ranks).
 
 The reference is single-GPU (test_hf.py:126 pins one device); every (batch,
 query head) is independent through all three steps of the operator
 (anchor_attn/src/ops/anchor_attn_v4.py:226-273), so this is the one natural
-partition and the all-gather its only exchange."""
+partition and the output exchange its only communication."""
 from __future__ import annotations
 
 from typing import Optional, Tuple

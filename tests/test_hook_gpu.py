@@ -108,7 +108,7 @@ def test_host_buffer_entry_point_matches_device_call(lib):
 
 
 def test_operator_replays_from_a_cuda_graph(lib):
-    """The five launches of one operator call can be captured into a CUDA graph (nothing in
+    """The launches of one operator call (six kernels, two small memsets) can be captured into a CUDA graph (nothing in
     the call allocates or synchronises) and replayed on new input values in the same buffers."""
     from anchor_attention_b200 import AnchorAttnCall
     Q, K, V = (t.cuda() for t in make_inputs(4096, 4, 2, seed=91, rope=True, q_shift=0.5))
