@@ -302,10 +302,13 @@ def anchor_attn_host(Q, K, V, out=None,
                      device=None):
     """``anchor_attn`` for tensors that live in (pinned) host memory: Q [B,H,N,D], K/V
     [B,Hkv,N,D] bf16 on the CPU in, ``out`` [B,H,N,D] on the CPU out (allocated pinned if
-    not given).  The KV-head groups are independent, so they are streamed: while group g
-    computes on the device, group g+1 is copied in and the result of group g-1 is copied
-    out, each on its own CUDA stream.  The call returns once ``out`` is complete.
-    Same arithmetic, head by head, as ``anchor_attn`` on device tensors."""
+    not given).  The KV-head groups are independent, so they are streamed: while one chunk
+    of query heads computes on the device, the next chunk is copied in and the result of
+    the previous one is copied out, each on its own CUDA stream.  A chunk is a whole KV
+    group, except that the first and the last group go head by head, so that the first
+    computation starts after one head's worth of queries (plus its K/V) has arrived and only
+    one head's output is left to copy when the last computation ends.  The call returns once
+    ``out`` is complete.  Same arithmetic, head by head, as ``anchor_attn`` on device tensors."""
     assert not Q.is_cuda and not K.is_cuda and not V.is_cuda, "anchor_attn_host takes host tensors"
     B, H, N, D = Q.shape
     Hkv = K.shape[1]
@@ -314,41 +317,53 @@ def anchor_attn_host(Q, K, V, out=None,
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     if out is None:
         out = torch.empty((B, H, N, D), dtype=Q.dtype).pin_memory()
+    # chunks: (KV group, first query head, number of heads)
+    chunks = []
+    for g in range(Hkv):
+        if g in (0, Hkv - 1) and Hg > 1:
+            chunks += [(g, g * Hg + i, 1) for i in range(Hg)]
+        else:
+            chunks.append((g, g * Hg, Hg))
     main = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     dq = [torch.empty((B, Hg, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
+    do = [torch.empty((B, Hg, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
     dk = [torch.empty((B, 1, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
     dv = [torch.empty((B, 1, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
-    do = [torch.empty((B, Hg, N, D), dtype=Q.dtype, device=dev) for _ in range(2)]
-    loaded = [torch.cuda.Event() for _ in range(2)]
-    computed = [torch.cuda.Event() for _ in range(2)]
-    drained = [torch.cuda.Event() for _ in range(2)]
+    n = len(chunks)
+    loaded = [torch.cuda.Event() for _ in range(n)]
+    computed = [torch.cuda.Event() for _ in range(n)]
+    drained = [torch.cuda.Event() for _ in range(n)]
+    last_chunk_of_group = {g: max(c for c, ch in enumerate(chunks) if ch[0] == g) for g in range(Hkv)}
 
-    def copy_in(g):
-        i = g & 1
+    def copy_in(c):
+        g, h0, nh = chunks[c]
         with torch.cuda.stream(s_in):
-            if g >= 2:
-                s_in.wait_event(computed[i])          # the buffers' previous user (group g-2) is done
-            dq[i].copy_(Q[:, g * Hg:(g + 1) * Hg], non_blocking=True)
-            dk[i].copy_(K[:, g:g + 1], non_blocking=True)
-            dv[i].copy_(V[:, g:g + 1], non_blocking=True)
-            loaded[i].record(s_in)
+            if c == 0 or chunks[c - 1][0] != g:                  # first chunk of its group: the group's K and V
+                if g >= 2:
+                    s_in.wait_event(computed[last_chunk_of_group[g - 2]])   # the K/V buffer's previous user
+                dk[g & 1].copy_(K[:, g:g + 1], non_blocking=True)
+                dv[g & 1].copy_(V[:, g:g + 1], non_blocking=True)
+            if c >= 2:
+                s_in.wait_event(computed[c - 2])                 # the query buffer's previous user
+            dq[c & 1][:, :nh].copy_(Q[:, h0:h0 + nh], non_blocking=True)
+            loaded[c].record(s_in)
 
     s_in.wait_stream(main)
     copy_in(0)
-    for g in range(Hkv):
-        i = g & 1
-        if g + 1 < Hkv:
-            copy_in(g + 1)
-        main.wait_event(loaded[i])
-        if g >= 2:
-            main.wait_event(drained[i])               # the output buffer has been copied out
-        AnchorAttnCall(dq[i], dk[i], dv[i], sm_scale, block_size, step, difference, out=do[i]).run()
-        computed[i].record(main)
+    for c, (g, h0, nh) in enumerate(chunks):
+        if c + 1 < n:
+            copy_in(c + 1)
+        main.wait_event(loaded[c])
+        if c >= 2:
+            main.wait_event(drained[c - 2])                      # the output buffer has been copied out
+        AnchorAttnCall(dq[c & 1][:, :nh], dk[g & 1], dv[g & 1], sm_scale, block_size, step, difference,
+                       out=do[c & 1][:, :nh]).run()
+        computed[c].record(main)
         with torch.cuda.stream(s_out):
-            s_out.wait_event(computed[i])
-            out[:, g * Hg:(g + 1) * Hg].copy_(do[i], non_blocking=True)
-            drained[i].record(s_out)
+            s_out.wait_event(computed[c])
+            out[:, h0:h0 + nh].copy_(do[c & 1][:, :nh], non_blocking=True)
+            drained[c].record(s_out)
     main.wait_stream(s_out)
     main.synchronize()
     return out
