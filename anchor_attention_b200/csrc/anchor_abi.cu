@@ -9,7 +9,14 @@
 #include <stdlib.h>
 #include <string.h>
 
+#ifndef AA_PERSISTENT
+#define AA_PERSISTENT 1
+#endif
+#ifndef AA_PERSISTENT_STEP3
+#define AA_PERSISTENT_STEP3 1
+#endif
 #include "attend_tc.cuh"
+#include "attend_persist.cuh"
 #include "block_list.cuh"
 #include "common.cuh"
 #include "gather.cuh"
@@ -264,10 +271,11 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
         // first pass of step 3: the tiles that are not runs go to the gather scratch once
         const int n_slots = gather_slots(p, lay);
         const int NB = p->N / (p->block_size * p->step);
+        // status words 2 and 3: the gather pass's slot counter and the persistent kernel's item counter
+        int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
+        e = cudaMemsetAsync(counter, 0, 2 * sizeof(int32_t), st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(step 3 counters)");
         if (n_slots > 0 && NB > 1) {
-            int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
-            e = cudaMemsetAsync(counter, 0, sizeof(int32_t), st);
-            if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(gather slot counter)");
             aa::GatherArgs ga;
             ga.k = ta.a.k;
             ga.v = ta.a.v;
@@ -293,6 +301,37 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
         memset(&vgmap, 0, sizeof(vgmap));
     }
     const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / (2 * aa::tc::kTile)));
+#if AA_PERSISTENT
+    if (MODE == aa::kWindow || (MODE == aa::kStripe && AA_PERSISTENT_STEP3)) {
+        // steps 1 and 3 run as one persistent CTA per SM when the query tensor has a tensor map
+        // (its tiles then arrive through the ring); the item counter (status word 3) is zero here:
+        // step 1's entry point has just cleared the status words, step 3 cleared it above
+        aa::tc::PersistArgs pa;
+        CUtensorMap qmap;
+        if (make_kv_map(&qmap, p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n, p->B, p->H, p->N, &pa.qpos_n, &pa.qpos_h,
+                        &pa.qpos_b) == AA_OK) {
+            static thread_local int persist_dev[2] = {-1, -1};
+            static thread_local int sm_count = 0;
+            constexpr int PM = MODE == aa::kWindow ? aa::kWindow : aa::kStripe;
+            if (persist_dev[PM] != dev) {
+                e = cudaFuncSetAttribute(aa::tc::attend_persist_kernel<PM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         aa::tc::kSmemTotal);
+                if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend_persist)");
+                e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+                if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(SM count)");
+                persist_dev[PM] = dev;
+            }
+            pa.item_counter = ws_ptr<int32_t>(p, lay.status_off) + 3;
+            pa.n_items = (int)grid;
+            const unsigned ctas = grid < (unsigned)sm_count ? grid : (unsigned)sm_count;
+            aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap,
+                                                                                                qmap, ta, pa);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (persistent)" : "launch step3 (persistent)");
+            return AA_OK;
+        }
+    }
+#endif
     aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, ta);
     e = cudaGetLastError();
     if (e != cudaSuccess)
