@@ -48,7 +48,7 @@ METRIC = "ms_per_layer_anchor_attn_prefill_128k_llama31_8b_heads"
 # GPU, from single-pass ncu captures of this benchmark (profiles/launch_list_seq131072.md): sequence
 # length -> (bytes, K/V tile-pair loads of 64 KB by all CTAs).  Other sizes, densities and per-rank
 # shares are scaled from the nearest entry by their tile-pair loads.
-STEP3_DRAM_CAPTURES = {32768: (1.247e9, 483840), 131072: (8.13e9, 8225280)}
+STEP3_DRAM_CAPTURES = {32768: (1.205e9, 483840), 131072: (7.583e9, 8225280)}
 
 
 def algorithmic_flops(N, H, counts_total, step=STEP):
