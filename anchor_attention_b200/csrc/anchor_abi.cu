@@ -9,12 +9,6 @@
 #include <stdlib.h>
 #include <string.h>
 
-#ifndef AA_PERSISTENT
-#define AA_PERSISTENT 1
-#endif
-#ifndef AA_PERSISTENT_STEP3
-#define AA_PERSISTENT_STEP3 1
-#endif
 #include "attend_tc.cuh"
 #include "attend_persist.cuh"
 #include "block_list.cuh"
@@ -222,15 +216,25 @@ struct DenseTail {
 template <int MODE>
 int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cudaStream_t st,
                      const aa_push_t* push = nullptr, int list_stride = 0, const DenseTail* dense = nullptr) {
-    static thread_local int configured_dev[3] = {-1, -1, -1};
+    // per thread and kernel: the device the kernel's shared-memory size was last raised on, and its SM count
+    static thread_local int configured_dev = -1;
+    static thread_local int sm_count = 0;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-    if (configured_dev[MODE] != dev) {
-        e = cudaFuncSetAttribute(aa::tc::attend_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 aa::tc::kSmemTotal);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend_tc)");
-        configured_dev[MODE] = dev;
+    if (configured_dev != dev) {
+        if (MODE == aa::kBlock) {
+            e = cudaFuncSetAttribute(aa::tc::attend_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     aa::tc::kSmemTotal);
+        } else {
+            constexpr int PM = MODE == aa::kWindow ? aa::kWindow : aa::kStripe;
+            e = cudaFuncSetAttribute(aa::tc::attend_persist_kernel<PM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     aa::tc::kSmemTotal);
+        }
+        if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attention kernel)");
+        e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(SM count)");
+        configured_dev = dev;
     }
     aa::tc::TcArgs ta;
     ta.a = attend_args(p, lay);
@@ -301,42 +305,28 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
         memset(&vgmap, 0, sizeof(vgmap));
     }
     const unsigned grid = (unsigned)((int64_t)p->B * p->H * (p->N / (2 * aa::tc::kTile)));
-#if AA_PERSISTENT
-    if (MODE == aa::kWindow || (MODE == aa::kStripe && AA_PERSISTENT_STEP3)) {
-        // steps 1 and 3 run as one persistent CTA per SM when the query tensor has a tensor map
-        // (its tiles then arrive through the ring); the item counter (status word 3) is zero here:
-        // step 1's entry point has just cleared the status words, step 3 cleared it above
-        aa::tc::PersistArgs pa;
-        CUtensorMap qmap;
-        if (make_kv_map(&qmap, p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n, p->B, p->H, p->N, &pa.qpos_n, &pa.qpos_h,
-                        &pa.qpos_b) == AA_OK) {
-            static thread_local int persist_dev[2] = {-1, -1};
-            static thread_local int sm_count = 0;
-            constexpr int PM = MODE == aa::kWindow ? aa::kWindow : aa::kStripe;
-            if (persist_dev[PM] != dev) {
-                e = cudaFuncSetAttribute(aa::tc::attend_persist_kernel<PM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         aa::tc::kSmemTotal);
-                if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(attend_persist)");
-                e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-                if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(SM count)");
-                persist_dev[PM] = dev;
-            }
-            pa.item_counter = ws_ptr<int32_t>(p, lay.status_off) + 3;
-            pa.n_items = (int)grid;
-            const unsigned ctas = grid < (unsigned)sm_count ? grid : (unsigned)sm_count;
-            aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap,
-                                                                                                qmap, ta, pa);
-            e = cudaGetLastError();
-            if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (persistent)" : "launch step3 (persistent)");
-            return AA_OK;
-        }
+    if (MODE == aa::kBlock) {
+        aa::tc::attend_block_kernel<<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, ta);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "launch block-sparse (tc)");
+        return AA_OK;
     }
-#endif
-    aa::tc::attend_tc_kernel<MODE><<<grid, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, ta);
+    // Steps 1 and 3: one persistent CTA per SM; the query tiles arrive through the ring, so the query
+    // tensor needs a tensor map like K and V.  The item counter (status word 3) is zero here: step 1's
+    // entry point has just cleared the status words, step 3 cleared it above.
+    constexpr int PM = MODE == aa::kWindow ? aa::kWindow : aa::kStripe;
+    aa::tc::PersistArgs pa;
+    CUtensorMap qmap;
+    rc = make_kv_map(&qmap, p->q, p->q_stride_b, p->q_stride_h, p->q_stride_n, p->B, p->H, p->N, &pa.qpos_n, &pa.qpos_h,
+                     &pa.qpos_b);
+    if (rc) return rc;
+    pa.item_counter = ws_ptr<int32_t>(p, lay.status_off) + 3;
+    pa.n_items = (int)grid;
+    const unsigned ctas = grid < (unsigned)sm_count ? grid : (unsigned)sm_count;
+    aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, qmap, ta,
+                                                                                        pa);
     e = cudaGetLastError();
-    if (e != cudaSuccess)
-        return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)"
-                                                : (MODE == aa::kStripe ? "launch step3 (tc)" : "launch block-sparse (tc)"));
+    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)" : "launch step3 (tc)");
     return AA_OK;
 }
 

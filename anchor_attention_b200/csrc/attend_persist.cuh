@@ -1,18 +1,36 @@
-// Steps 1 and 3 as PERSISTENT CTAs: one CTA per SM walks the work items (256 query rows of one
-// head each, heaviest first) that attend_tc.cuh gives to one CTA each.  Same arithmetic, same
-// tile order, same results bit for bit; what changes is what an SM does between two items.
+// Steps 1 and 3 of the operator on the Blackwell tensor cores, as PERSISTENT CTAs: one CTA per SM
+// walks work items of 256 query rows of one head (two 128-row tiles A and B that lie in the same
+// big block and therefore share their key/value tiles), heaviest first, and for each item a list
+// of 128-row key/value tiles:
 //
-// Why: a kernel that allocates tensor memory gets one resident CTA per SM, so with one CTA per
-// item nothing overlaps an item's start-up (launch, barrier and tensor-memory set-up, the
+//   kWindow  (step 1)  contiguous tiles of [0, min(G, end)) U [max(b*G, that), end),
+//            end = last query row + 1; additive -1e6 causal mask on diagonal tiles;
+//            query scaled with dtype-rounded constants; writes M, L, Acc (Acc in 128-row
+//            chunk-major tiles, see acc_tile()).
+//            Reference: anchor_attn/src/ops/anchor_step_1_2_v2.py:8-161.
+//   kStripe  (step 3)  tiles of 128 ids from the big block's id list; state starts
+//            from step 1's (M, L, Acc); slots past the count masked to -inf;
+//            writes bf16(acc / l).  Reference: anchor_attn/src/ops/anchor_attn_v4.py:7-105.
+//
+// Warp roles, tensor-memory layout and the lazily moved exponent reference are those of
+// attend_tc.cuh.  The loaders (warps 9-11) fill the 5-slot ring of 32 KB tiles with: one TMA box
+// load for a run of 128 consecutive rows; one bulk copy for a tile the gather pass (gather.cuh)
+// put into scratch; discrete rows without a scratch slot split between TMA row gathers
+// (tile::gather4, four rows per instruction, warp 9) and 16-byte cp.async copies (warps 10-11; all
+// three warps for stride patterns no 2-D tensor map covers).
+//
+// Why persistent: a kernel that allocates tensor memory gets one resident CTA per SM, so with one
+// CTA per item nothing overlaps an item's start-up (launch, barrier and tensor-memory set-up, the
 // query tile and, in step 3, the 128 KB of step-1 state arriving from DRAM) or its tail (the
 // output leaving).  With short key lists -- step 1 always, step 3 at low density -- those two
 // are a large part of an item.  Here
 //   * tensor memory, barriers and register re-allocation are set up once per SM;
 //   * an item's query tiles and (step 3) its accumulator tiles are fetched by the loader warps
-//     through the same 5-slot ring as the key/value tiles, as asynchronous bulk copies that run
+//     through the same ring as the key/value tiles, as asynchronous bulk copies that run
 //     while the previous item is still being computed and written out;
 //   * items are handed out by an atomic counter, each shortly before the previous one ends, through
-//     a two-entry queue in shared memory, so the hardware's dynamic CTA scheduling is kept.
+//     a two-entry queue in shared memory, so that items start in order on whichever SM is free, as
+//     CTAs of a grid would.
 //
 // Ring entries of one item, in order (each 32 KB):
 //   step 1:                Q_A Q_B                      K_0 V_0 K_1 V_1 ...
@@ -646,8 +664,12 @@ __device__ __forceinline__ void persist_loader(const CUtensorMap* kmap, const CU
                 }
                 continue;
             }
-            // discrete rows without a scratch slot: TMA row gathers from the first loader warp,
-            // 16-byte cp.async copies from the others (see attend_tc.cuh)
+            // Discrete rows without a scratch slot.  The TMA unit and the load/store unit each sustain
+            // only about one 128-byte row segment per 17-24 cycles on gathers, so the tile is split
+            // between them: rows [0, tma_rows) by TMA row gathers from the first loader warp (lane i takes
+            // rows 4i .. 4i+3, two 64-column halves each), the rest by 16-byte cp.async copies from the
+            // other loader warps; without a usable 2-D map all loader warps copy.  Slots past the count
+            // read row 0 / zero-fill; the softmax masks them.
             const bool g4 = is_v ? ta.v_gather : ta.k_gather;
             const int tma_rows = g4 ? kTmaRows : 0;
             int ra, rb;
