@@ -124,9 +124,9 @@ struct SoftmaxCtx {
     uint32_t tmem_base;
     volatile int* abort_flag;
     uint32_t q_full[2], s_full[2], o_done[2], p_part[2][4];
-    int pair, z, h, hz, ntiles;
+    int pair, z, h, ntiles;
     const int32_t* list;             // the pair's tile list
-    int dense_last0;                 // kBlock, dense variant: last key block of the pair's first query tile
+    int dense_last0;                 // dense variant: last key block of the pair's first query tile
 };
 
 // The softmax role of warps 0-7 (see the file header): thread r of tile j owns query row r.
@@ -136,7 +136,7 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     uint8_t* smem = cx.smem;
     const uint32_t tmem_base = cx.tmem_base;
     volatile int* abort_flag = cx.abort_flag;
-    const int pair = cx.pair, z = cx.z, h = cx.h, hz = cx.hz;
+    const int pair = cx.pair, z = cx.z, h = cx.h;
     const int ntiles = cx.ntiles;
     const int j = warp >> 2;
     const uint32_t q_full_j = cx.q_full[j], s_full_j = cx.s_full[j], o_done_j = cx.o_done[j];
@@ -145,8 +145,6 @@ __device__ __forceinline__ void softmax_role(const TcArgs& ta, const SoftmaxCtx&
     for (int q = 0; q < kPParts; ++q) p_part_j[q] = cx.p_part[j][q];
     const int r = tid & 127;
     const int qb = 2 * pair + j;
-    const int row_g = qb * kTile + r;
-    (void)row_g; (void)hz;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + (uint32_t)j * 128u;
     const uint32_t tO = tmem_base + lane_base + 256u + (uint32_t)j * 128u;
@@ -434,7 +432,7 @@ attend_block_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
             for (int q = 0; q < 4; ++q) sc.p_part[jj][q] = p_part(jj, q);
             sc.o_done[jj] = o_done(jj);
         }
-        sc.pair = pair; sc.z = z; sc.h = h; sc.hz = hz;
+        sc.pair = pair; sc.z = z; sc.h = h;
         sc.ntiles = ntiles;
         sc.list = idp;
         sc.dense_last0 = dense_last0;
