@@ -99,3 +99,33 @@ def test_token_sharded_push_from_persistent_items(lib):
     call2.check_status()
     assert torch.equal(shares[0], want[:, :, :half])
     assert torch.equal(shares[1], want[:, :, half:])
+
+
+def test_two_streams_at_once(lib):
+    """Two operator calls in flight on two streams, each with its own workspace: both grids are one
+    CTA per SM and each SM holds one such CTA, so the second kernel's CTAs start as the first one's
+    leave; nothing waits on another CTA, and both results equal the calls made one after the other."""
+    probs = [(12288, 4, 2, 10.0, 31), (8192, 8, 2, 9.0, 32)]
+    inputs = [tuple(t.cuda() for t in make_inputs(N, H, Hkv, seed=seed, rope=True, q_shift=0.5))
+              for N, H, Hkv, _, seed in probs]
+    from anchor_attention_b200 import AnchorAttnCall
+    want = [AnchorAttnCall(*inp, None, 128, 16, p[3]).run().clone() for inp, p in zip(inputs, probs)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    calls = []
+    for s, inp, p in zip(streams, inputs, probs):
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            calls.append(AnchorAttnCall(*inp, None, 128, 16, p[3]))
+    for rep in range(3):                       # interleave the launches of the two calls
+        for s, c in zip(streams, calls):
+            with torch.cuda.stream(s):
+                c.step1()
+        for s, c in zip(streams, calls):
+            with torch.cuda.stream(s):
+                c.step2()
+                c.step3()
+    torch.cuda.synchronize()
+    for c, w in zip(calls, want):
+        c.check_status()
+        assert torch.equal(c.out, w)
