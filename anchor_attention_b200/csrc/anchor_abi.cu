@@ -272,32 +272,6 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     CUtensorMap kgmap, vgmap;
     ta.k_gather = ta.v_gather = 0;
     if (MODE == aa::kStripe) {
-        // first pass of step 3: the tiles that are not runs go to the gather scratch once
-        const int n_slots = gather_slots(p, lay);
-        const int NB = p->N / (p->block_size * p->step);
-        // status words 2 and 3: the gather pass's slot counter and the persistent kernel's item counter
-        int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
-        e = cudaMemsetAsync(counter, 0, 2 * sizeof(int32_t), st);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(step 3 counters)");
-        if (n_slots > 0 && NB > 1) {
-            aa::GatherArgs ga;
-            ga.k = ta.a.k;
-            ga.v = ta.a.v;
-            ga.counts = ta.a.counts;
-            ga.ids = ta.a.ids;
-            ga.ids_per_head = lay.ids_per_head;
-            ga.tile_slot = ws_ptr<int32_t>(p, lay.tile_slot_off);
-            ga.scratch = ws_ptr<uint8_t>(p, lay.gather_off);
-            ga.slot_counter = counter;
-            ga.n_slots = n_slots;
-            ga.H = p->H; ga.Hkv = p->Hkv; ga.N = p->N; ga.step = p->step; ga.block = p->block_size;
-            aa::gather_tiles_kernel<<<dim3(aa::kGatherSplit, NB - 1, p->B * p->H), aa::kGatherThreads, 0, st>>>(ga);
-            e = cudaGetLastError();
-            if (e != cudaSuccess) return cuda_fail(e, "launch gather pass");
-            ta.tile_slot = ga.tile_slot;
-            ta.gather = ga.scratch;
-            ta.n_slots = n_slots;
-        }
         make_gather_map(&kgmap, p->k, p->k_stride_b, p->k_stride_h, p->k_stride_n, p->B, p->Hkv, p->N, &ta.k_gather);
         make_gather_map(&vgmap, p->v, p->v_stride_b, p->v_stride_h, p->v_stride_n, p->B, p->Hkv, p->N, &ta.v_gather);
     } else {
@@ -321,12 +295,94 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
                      &pa.qpos_b);
     if (rc) return rc;
     pa.item_counter = ws_ptr<int32_t>(p, lay.status_off) + 3;
-    pa.n_items = (int)grid;
-    const unsigned ctas = grid < (unsigned)sm_count ? grid : (unsigned)sm_count;
-    aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, qmap, ta,
-                                                                                        pa);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, MODE == aa::kWindow ? "launch step1 (tc)" : "launch step3 (tc)");
+    if (MODE == aa::kWindow) {
+        pa.n_items = (int)grid;
+        const unsigned ctas = grid < (unsigned)sm_count ? grid : (unsigned)sm_count;
+        aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, qmap,
+                                                                                            ta, pa);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "launch step1 (tc)");
+        return AA_OK;
+    }
+
+    // Step 3 = gather pass (the tiles that are not runs go to the gather scratch once) + attention.
+    // When the scratch has a slot for every tile any list COULD have, that is one pass and one launch.
+    // Otherwise whether the slots suffice is only known on the device (a tile without a slot is gathered
+    // by each of the eight CTAs that read it, at a third of the speed): plan_step3_kernel decides, from the
+    // counts, between that same sequence and one that goes KV head by KV head (or several at a time) with
+    // the scratch reused; both sequences are launched and the kernels of the other one leave at once.
+    // Status words 2 and 3 (slot counter, item counter) are set before each part, word 4 is the plan.
+    const int n_slots = gather_slots(p, lay);
+    const int NB = p->N / (p->block_size * p->step);
+    const int Hg = p->H / p->Hkv;
+    const int per_kv = Hg * (p->N / (2 * aa::tc::kTile));
+    const int kv_total = p->B * p->Hkv;
+    const int64_t tiles_per_kv = (int64_t)Hg * (lay.ids_per_head / aa::tc::kTile);
+    const bool gather = n_slots > 0 && NB > 1;
+    const bool may_overflow = gather && kv_total > 1 && (int64_t)n_slots < tiles_per_kv * kv_total;
+    int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
+    int32_t* plan = ws_ptr<int32_t>(p, lay.status_off) + 4;
+    if (gather) {
+        ta.tile_slot = ws_ptr<int32_t>(p, lay.tile_slot_off);
+        ta.gather = ws_ptr<uint8_t>(p, lay.gather_off);
+        ta.n_slots = n_slots;
+    }
+    if (may_overflow) {
+        aa::plan_step3_kernel<<<1, 256, 0, st>>>(ta.a.counts, p->B * p->H * NB, NB, p->block_size * p->step, p->block_size,
+                                                 n_slots, plan);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "launch step 3 plan");
+    }
+    // one part: KV heads k0 .. k1 - 1
+    auto run_part = [&](int k0, int k1, const int32_t* plan_word, int run_if) -> int {
+        // the item counter starts at the part's first item; the kernel draws until it reaches the last
+        cudaError_t err = cudaSuccess;
+        if (!plan_word && k0 == 0) {
+            err = cudaMemsetAsync(counter, 0, 2 * sizeof(int32_t), st);
+            if (err != cudaSuccess) return cuda_fail(err, "cudaMemsetAsync(step 3 counters)");
+        } else {
+            aa::arm_step3_kernel<<<1, 32, 0, st>>>(counter, plan_word, run_if, k0 * per_kv);
+            err = cudaGetLastError();
+            if (err != cudaSuccess) return cuda_fail(err, "launch step 3 arm");
+        }
+        if (gather) {
+            aa::GatherArgs ga;
+            ga.k = ta.a.k;
+            ga.v = ta.a.v;
+            ga.counts = ta.a.counts;
+            ga.ids = ta.a.ids;
+            ga.ids_per_head = lay.ids_per_head;
+            ga.tile_slot = ws_ptr<int32_t>(p, lay.tile_slot_off);
+            ga.scratch = ws_ptr<uint8_t>(p, lay.gather_off);
+            ga.slot_counter = counter;
+            ga.n_slots = n_slots;
+            ga.hz0 = k0 * Hg;
+            ga.plan = plan_word;
+            ga.run_if = run_if;
+            ga.H = p->H; ga.Hkv = p->Hkv; ga.N = p->N; ga.step = p->step; ga.block = p->block_size;
+            aa::gather_tiles_kernel<<<dim3(aa::kGatherSplit, NB - 1, (k1 - k0) * Hg), aa::kGatherThreads, 0, st>>>(ga);
+            err = cudaGetLastError();
+            if (err != cudaSuccess) return cuda_fail(err, "launch gather pass");
+        }
+        pa.n_items = k1 * per_kv;
+        const int part_items = (k1 - k0) * per_kv;
+        const unsigned ctas = part_items < sm_count ? (unsigned)part_items : (unsigned)sm_count;
+        aa::tc::attend_persist_kernel<PM><<<ctas, aa::tc::kThreads, aa::tc::kSmemTotal, st>>>(kmap, vmap, kgmap, vgmap, qmap,
+                                                                                            ta, pa);
+        err = cudaGetLastError();
+        if (err != cudaSuccess) return cuda_fail(err, "launch step3 (tc)");
+        return AA_OK;
+    };
+    rc = run_part(0, kv_total, may_overflow ? plan : nullptr, 0);
+    if (rc) return rc;
+    if (may_overflow) {
+        int kv_per_part = (int)(n_slots / tiles_per_kv);
+        if (kv_per_part < 1) kv_per_part = 1;
+        for (int k0 = 0; k0 < kv_total; k0 += kv_per_part) {
+            rc = run_part(k0, k0 + kv_per_part < kv_total ? k0 + kv_per_part : kv_total, plan, 1);
+            if (rc) return rc;
+        }
+    }
     return AA_OK;
 }
 
@@ -434,7 +490,7 @@ int aa_workspace_layout(const aa_params_t* p, aa_workspace_layout_t* lay) {
     lay->bitmap_off = off;  off = align_up(off + BH * NB * (N / 32) * sizeof(uint32_t));
     lay->counts_off = off;  off = align_up(off + BH * NB * sizeof(int32_t));
     lay->ids_off = off;     off = align_up(off + BH * (size_t)lay->ids_per_head * sizeof(int32_t) + 256);
-    lay->status_off = off;  off = align_up(off + 4 * sizeof(int32_t));
+    lay->status_off = off;  off = align_up(off + 8 * sizeof(int32_t));
     const size_t tiles = BH * (size_t)(lay->ids_per_head / aa::tc::kTile);
     lay->tile_slot_off = off;  off = align_up(off + tiles * sizeof(int32_t) + 256);
     lay->gather_off = off;

@@ -38,6 +38,9 @@ struct GatherArgs {
     uint8_t* scratch;                    // n_slots x 64 KB, 1024-byte aligned
     int32_t* slot_counter;               // zero before the launch
     int n_slots;
+    int hz0;                             // first (batch, head) of this launch: blockIdx.z counts from it
+    const int32_t* plan;                 // NULL, or: the launch only runs when *plan == run_if (plan_step3_kernel)
+    int run_if;
     int H, Hkv, N, step, block;
 };
 
@@ -46,10 +49,11 @@ __device__ __forceinline__ int64_t id_row_offset(int G, int block, int b) {
     return (b == 0) ? 0 : ((int64_t)G * b * (b - 1) / 2 - 2 * (int64_t)block * (b - 1));
 }
 
-// grid (kGatherSplit, NB - 1, B * H); big block b = blockIdx.y + 1
+// grid (kGatherSplit, NB - 1, heads of the launch); big block b = blockIdx.y + 1
 __global__ void __launch_bounds__(kGatherThreads) gather_tiles_kernel(GatherArgs a) {
     constexpr int kTileRows = 128, kImage = kTileRows * kRowBytes, kSlab = kImage / 2;
-    const int b = blockIdx.y + 1, hz = blockIdx.z;
+    if (a.plan && *a.plan != a.run_if) return;
+    const int b = blockIdx.y + 1, hz = a.hz0 + blockIdx.z;
     const int z = hz / a.H, h = hz % a.H, kvh = h / (a.H / a.Hkv);
     const int G = a.block * a.step, NB = a.N / G;
     const int cap = b * G - 2 * a.block;
@@ -109,6 +113,48 @@ __global__ void __launch_bounds__(kGatherThreads) gather_tiles_kernel(GatherArgs
             *reinterpret_cast<uint4*>(dst + kImage + off) = vx[i];
         }
     }
+}
+
+// ---------------------------------------------------------------------------
+// How step 3 runs when the scratch cannot hold a slot for every tile that any list COULD have:
+// *plan = 0 -> the lists at hand need no more than n_slots slots (tiles of the lists that are not
+// full; a full list is all runs), everything goes in one gather pass and one attention launch;
+// *plan = 1 -> KV head by KV head, the scratch reused.  Both sequences are launched; the kernels of
+// the one that was not chosen leave at once (the gather pass reads *plan, the attention kernel
+// finds its item counter exhausted: arm_step3_kernel).  One block of 256 threads.
+// ---------------------------------------------------------------------------
+// Sets the two counters of one part of step 3 (the status words at `counters`).  A part that is to run
+// (no plan, or *plan == run_if): slot counter 0, item counter at the part's first item.  A part that is
+// not: item counter beyond any item, so that the attention kernel's CTAs find nothing to draw and leave;
+// the slot counter keeps what the sequence that did run left in it.
+__global__ void arm_step3_kernel(int32_t* counters, const int32_t* plan, int run_if, int first_item) {
+    if (threadIdx.x == 0) {
+        if (!plan || *plan == run_if) {
+            counters[0] = 0;
+            counters[1] = first_item;
+        } else {
+            counters[1] = 0x7F000000;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) plan_step3_kernel(const int32_t* __restrict__ counts, int n_lists, int NB, int G,
+                                                         int block, int n_slots, int32_t* plan) {
+    __shared__ unsigned long long part[256];
+    unsigned long long tiles = 0;
+    for (int i = threadIdx.x; i < n_lists; i += blockDim.x) {
+        const int b = i % NB;
+        const int cap = max(b * G - 2 * block, 0);
+        const int count = min(max(counts[i], 0), cap);
+        if (count < cap) tiles += (unsigned long long)((count + 127) / 128);
+    }
+    part[threadIdx.x] = tiles;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) part[threadIdx.x] += part[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *plan = part[0] > (unsigned long long)n_slots ? 1 : 0;
 }
 
 // ---------------------------------------------------------------------------

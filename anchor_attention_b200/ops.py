@@ -165,7 +165,8 @@ class AnchorAttnCall:
 
     @property
     def gather_slots_used(self) -> int:
-        """64 KB gather slots step 3 handed out in its last run (synchronises)."""
+        """64 KB gather slots step 3 handed out in its last run (synchronises); when that run went KV head
+        by KV head (status word 4), those of its last part."""
         return int(self._view(self.layout.status_off, 4, torch.int32)[2])
 
     # ---- typed views of the workspace ----------------------------------

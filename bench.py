@@ -606,7 +606,10 @@ def run_triton_bar(args):
     import torch
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    line = {"leg": "triton_bar", "seq": args.seq, "heads": f"{H}q/{HKV}kv", "theta": THETA}
+    theta = args.theta
+    line = {"leg": "triton_bar", "seq": args.seq, "heads": f"{H}q/{HKV}kv", "theta": theta}
+    if args.q_shift != 0.0 or theta != THETA:
+        line["data"] = f"synthetic, AUXILIARY distribution (q_shift {args.q_shift}, theta {theta})"
     root = args.ref_root
     if not root or not os.path.isdir(root):
         line["triton_bar"] = f"unavailable: no reference checkout at {root!r} (pass --ref-root)"
@@ -623,7 +626,7 @@ def run_triton_bar(args):
     from anchor_attention_b200.synthetic import make_inputs
     dev = torch.device("cuda", 0)
     N = args.seq
-    Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev)
+    Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, q_shift=args.q_shift)
     Ke, Ve = (t.repeat_interleave(H // HKV, dim=1).contiguous() for t in (K, V))
 
     def ev():
@@ -634,13 +637,13 @@ def run_triton_bar(args):
     for i in range(3 + args.steps):
         a, b = ev(), ev()
         a.record()
-        out_ref, ratio, s_ms, c_ms = ref.anchor_attn_test_time(Q, Ke, Ve, None, BLOCK, STEP, THETA, True)
+        out_ref, ratio, s_ms, c_ms = ref.anchor_attn_test_time(Q, Ke, Ve, None, BLOCK, STEP, theta, True)
         b.record()
         torch.cuda.synchronize()
         if i >= 3:
             full.append(a.elapsed_time(b)); search.append(s_ms); compute.append(c_ms)
     del Ke, Ve
-    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA)
+    call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, theta)
     ours = []
     for i in range(3 + args.steps):
         a, b = ev(), ev()

@@ -96,11 +96,14 @@ typedef struct aa_workspace_layout {
     size_t bitmap_off;   /* uint32  [B,H,NB,N/32]    hit bitmap of step 2                       */
     size_t counts_off;   /* int32   [B,H,NB]         selected columns per big block             */
     size_t ids_off;      /* int32   [B,H,ids_per_head] ascending selected column ids            */
-    size_t status_off;   /* int32   [4]              [0] a bounded device-side wait gave up,
+    size_t status_off;   /* int32   [8]              [0] a bounded device-side wait gave up,
                                                      [1] aa_validate_lists found a bad list,
                                                      [2] gather slots handed out by step 3,
-                                                     [3] work items handed out by the step-1 or
-                                                         step-3 kernel that ran last             */
+                                                     [3] item counter of the step-1 or step-3
+                                                         kernel that ran last,
+                                                     [4] step 3 ran KV head by KV head (1) or in
+                                                         one go (0); only written when the gather
+                                                         scratch has no slot for every possible tile */
     size_t total_bytes;  /* recommended workspace size: min_bytes + gather_bytes                 */
     int64_t ids_per_head;
     size_t tile_slot_off;/* int32   [B,H,ids_per_head/128] gather slot of every 128-id tile, or -1 */

@@ -129,3 +129,35 @@ def test_two_streams_at_once(lib):
     for c, w in zip(calls, want):
         c.check_status()
         assert torch.equal(c.out, w)
+
+
+def test_step3_goes_kv_head_by_kv_head_when_the_lists_outgrow_the_scratch(lib):
+    """A gather scratch too small for every tile any list could have: the plan kernel looks at the
+    counts.  Lists that need more slots than there are -> step 3 runs KV head by KV head with the
+    scratch reused (status word 4 = 1); lists that fit, or full lists (all runs) -> one go (0).
+    Same bits as with the recommended workspace in every case."""
+    from anchor_attention_b200 import AnchorAttnCall
+    N, H, Hkv = 8192, 8, 4
+    for theta, shift, slots, want_plan in ((10.0, 0.5, 40, 1),      # hundreds of gathered tiles, 40 slots
+                                           (12.0, 0.0, 40, 0),      # full lists: no slot needed
+                                           (8.5, 0.5, 400, 0)):     # short lists: a few dozen tiles fit
+        Q, K, V = (t.cuda() for t in make_inputs(N, H, Hkv, seed=77, rope=True, q_shift=shift))
+        ref_call = AnchorAttnCall(Q, K, V, None, 128, 16, theta)
+        want = ref_call.run().clone()
+        ref_call.check_status()
+        need = int(sum((int(c) + 127) // 128 for b, row in enumerate(ref_call.counts[0].t().tolist()) for c in row
+                       if c < max(b * 2048 - 256, 0)))
+        probe = AnchorAttnCall(Q, K, V, None, 128, 16, theta)
+        nbytes = probe.layout.min_bytes + slots * 65536
+        call = AnchorAttnCall(Q, K, V, None, 128, 16, theta,
+                              workspace=torch.empty(nbytes, dtype=torch.uint8, device="cuda"))
+        out = call.run()
+        call.check_status()
+        st = _status_words_n(call, 5)
+        assert st[4] == want_plan, (theta, need, slots, st)
+        assert (need > slots) == bool(want_plan), (theta, need, slots)
+        assert torch.equal(out, want)
+
+
+def _status_words_n(call, n):
+    return call._view(call.layout.status_off, n, torch.int32).cpu().tolist()
