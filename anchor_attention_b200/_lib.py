@@ -16,7 +16,7 @@ EXPORTS = [
     "aa_workspace_bytes", "aa_workspace_layout", "aa_id_row_offset", "aa_forward",
     "aa_step1_anchor", "aa_step2_stripes", "aa_step3_sparse", "aa_check_status",
     "aa_total_selected", "aa_strerror", "aa_last_cuda_error", "aa_version",
-    "aa_launches_per_forward", "aa_step2_stripes_static", "aa_step3_sparse_push",
+    "aa_launches_per_forward", "aa_forward_launches", "aa_step2_stripes_static", "aa_step3_sparse_push",
     "aa_selftest_wait_timeout", "aa_block_sparse_workspace_bytes", "aa_block_sparse_attend",
     "aa_block_sparse_check_status", "aa_validate_lists", "aa_step2_stripes_static_check_status",
     "aa_peer_barrier", "aa_dense_causal_attend", "aa_rope_dispatch",
@@ -151,6 +151,8 @@ def load():
         getattr(lib, name).argtypes = [PB, ctypes.c_void_p]
         getattr(lib, name).restype = ctypes.c_int
     lib.aa_total_selected.argtypes = [P, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
+    lib.aa_forward_launches.argtypes = [P]
+    lib.aa_forward_launches.restype = ctypes.c_int
     lib.aa_strerror.argtypes = [ctypes.c_int]
     lib.aa_strerror.restype = ctypes.c_char_p
     lib.aa_last_cuda_error.restype = ctypes.c_char_p

@@ -60,6 +60,30 @@ int check_full(const aa_params_t* p, aa_workspace_layout_t* lay) {
     return AA_OK;
 }
 
+// How step 3 is laid out for a problem and workspace: whether there is a gather pass at all, whether
+// the scratch may be too small for the lists (then the device decides between one go and parts), and how
+// many KV heads one part takes.
+struct Step3Layout {
+    int n_slots, kv_total, kv_per_part;
+    bool gather, may_overflow;
+};
+int gather_slots(const aa_params_t* p, const aa_workspace_layout_t& lay);
+Step3Layout step3_layout(const aa_params_t* p, const aa_workspace_layout_t& lay) {
+    Step3Layout s;
+    s.n_slots = gather_slots(p, lay);
+    const int NB = p->N / (p->block_size * p->step);
+    const int64_t tiles_per_kv = (int64_t)(p->H / p->Hkv) * (lay.ids_per_head / aa::tc::kTile);
+    s.kv_total = p->B * p->Hkv;
+    s.gather = s.n_slots > 0 && NB > 1;
+    s.may_overflow = s.gather && s.kv_total > 1 && (int64_t)s.n_slots < tiles_per_kv * s.kv_total;
+    s.kv_per_part = s.kv_total;
+    if (s.may_overflow) {
+        s.kv_per_part = (int)(s.n_slots / tiles_per_kv);
+        if (s.kv_per_part < 1) s.kv_per_part = 1;
+    }
+    return s;
+}
+
 // 64 KB gather slots the caller's workspace holds beyond the mandatory sections
 int gather_slots(const aa_params_t* p, const aa_workspace_layout_t& lay) {
     const size_t have = (p->workspace_bytes - lay.gather_off) / (2 * (size_t)aa::tc::kTileBytes);
@@ -312,14 +336,12 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     // counts, between that same sequence and one that goes KV head by KV head (or several at a time) with
     // the scratch reused; both sequences are launched and the kernels of the other one leave at once.
     // Status words 2 and 3 (slot counter, item counter) are set before each part, word 4 is the plan.
-    const int n_slots = gather_slots(p, lay);
+    const Step3Layout s3 = step3_layout(p, lay);
+    const int n_slots = s3.n_slots, kv_total = s3.kv_total;
+    const bool gather = s3.gather, may_overflow = s3.may_overflow;
     const int NB = p->N / (p->block_size * p->step);
     const int Hg = p->H / p->Hkv;
     const int per_kv = Hg * (p->N / (2 * aa::tc::kTile));
-    const int kv_total = p->B * p->Hkv;
-    const int64_t tiles_per_kv = (int64_t)Hg * (lay.ids_per_head / aa::tc::kTile);
-    const bool gather = n_slots > 0 && NB > 1;
-    const bool may_overflow = gather && kv_total > 1 && (int64_t)n_slots < tiles_per_kv * kv_total;
     int32_t* counter = ws_ptr<int32_t>(p, lay.status_off) + 2;
     int32_t* plan = ws_ptr<int32_t>(p, lay.status_off) + 4;
     if (gather) {
@@ -376,8 +398,7 @@ int launch_attend_tc(const aa_params_t* p, const aa_workspace_layout_t& lay, cud
     rc = run_part(0, kv_total, may_overflow ? plan : nullptr, 0);
     if (rc) return rc;
     if (may_overflow) {
-        int kv_per_part = (int)(n_slots / tiles_per_kv);
-        if (kv_per_part < 1) kv_per_part = 1;
+        const int kv_per_part = s3.kv_per_part;
         for (int k0 = 0; k0 < kv_total; k0 += kv_per_part) {
             rc = run_part(k0, k0 + kv_per_part < kv_total ? k0 + kv_per_part : kv_total, plan, 1);
             if (rc) return rc;
@@ -1003,5 +1024,17 @@ const char* aa_strerror(int code) {
 const char* aa_last_cuda_error(void) { return g_cuda_err; }
 int aa_version(void) { return 2; }
 int aa_launches_per_forward(void) { return 6; }
+int aa_forward_launches(const aa_params_t* p) {
+    aa_workspace_layout_t lay;
+    int rc = check_full(p, &lay);
+    if (rc) return rc < 0 ? rc : -rc;
+    const Step3Layout s3 = step3_layout(p, lay);
+    const int NB = p->N / (p->block_size * p->step);
+    int n = 1 + 2 + (NB > 1 ? 1 : 0);                       // step 1; pool, compact and (with candidates) the score kernel
+    if (!s3.gather) return n + 1;                           // step 3: the attention kernel alone
+    if (!s3.may_overflow) return n + 2;                     // gather pass + attention kernel
+    const int parts = (s3.kv_total + s3.kv_per_part - 1) / s3.kv_per_part;
+    return n + 1 + 3 * (1 + parts);                         // plan; counters, gather pass, attention kernel per sequence part
+}
 
 }  // extern "C"

@@ -164,6 +164,15 @@ class AnchorAttnCall:
         self._call(self._lib.aa_validate_lists)
 
     @property
+    def launches(self) -> int:
+        """Kernels of the library one ``run()`` of this call enqueues (step 3 enqueues both of its
+        sequences when the gather scratch has no slot for every possible tile)."""
+        n = _lib.load().aa_forward_launches(ctypes.byref(self.params))
+        if n < 0:
+            raise RuntimeError(f"aa_forward_launches: {_lib.error_text(-n)}")
+        return n
+
+    @property
     def gather_slots_used(self) -> int:
         """64 KB gather slots step 3 handed out in its last run (synchronises); when that run went KV head
         by KV head (status word 4), those of its last part."""
@@ -412,4 +421,5 @@ def dense_causal_attention(query, key, value, scaling: float = None, out: Option
 
 
 def launches_per_forward() -> int:
+    """Kernels of the library one operator call enqueues, at least (see ``AnchorAttnCall.launches``)."""
     return _lib.load().aa_launches_per_forward()

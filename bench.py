@@ -394,7 +394,7 @@ def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from anchor_attention_b200 import AnchorAttnCall, launches_per_forward
+    from anchor_attention_b200 import AnchorAttnCall
     from anchor_attention_b200.parallel import HeadShardedAnchorAttn, PushedOutput, gather_heads, head_partition
     from anchor_attention_b200.synthetic import make_inputs
 
@@ -571,7 +571,10 @@ def run_ours(args):
                          "peak_source": f"{peak_src} (sustained bf16)", "launch_ms": k3_ms},
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": W * sum(t.numel() * 2 for t in (hq, hk, hv)),
                     "d2h_bytes_per_step": W * hout.numel() * 2, "steps": e2e_steps, "equals_device_result": e2e_equal},
-            "gpu_launches": launches_per_forward() * args.steps,
+            # this rank's kernels of the library in the timed region: the operator's own (step 3 enqueues both
+            # of its sequences when the gather scratch has no slot for every possible tile; the kernels of the
+            # one the device does not choose leave at once) plus, head-parallel, the flag barrier
+            "gpu_launches": (call.launches + (1 if push else 0)) * args.steps,
             "device_status": device_status,
             "clocks": clocks,
         }

@@ -357,9 +357,13 @@ int aa_dense_causal_attend(const aa_dense_causal_t *a, void *stream);
 const char *aa_strerror(int code);
 /* Text of the last CUDA error this library saw on the calling thread. */
 const char *aa_last_cuda_error(void);
-/* Library version, and how many of the library's kernels one aa_forward enqueues. */
+/* Library version, and how many of the library's kernels one aa_forward enqueues: the least (a
+ * workspace whose gather scratch has a slot for every possible tile), and the number for a given
+ * problem and workspace (step 3 then also enqueues its plan kernel and both of its sequences, of
+ * which the kernels of one leave at once; < 0: an error code).  No counterpart in the reference. */
 int aa_version(void);
 int aa_launches_per_forward(void);
+int aa_forward_launches(const aa_params_t *p);
 
 #ifdef __cplusplus
 }

@@ -261,3 +261,33 @@ def test_new_entry_points_validate_before_touching_cuda(lib):
     assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
     push.rows_per_peer = 2048                                           # 2 x 2048 rows do not cover N = 8192
     assert lib.aa_step3_sparse_push(ctypes.byref(p), ctypes.byref(push), None) == -2
+
+
+def test_forward_launch_count_follows_the_step3_layout(lib):
+    """aa_forward_launches only looks at sizes: with a slot for every possible tile step 3 is a gather
+    pass and one attention launch (6 kernels in all); without any scratch the attention kernel alone;
+    with a scratch that the lists may outgrow, the plan kernel plus both sequences."""
+    import ctypes
+
+    def count(N, H, Hkv, scratch):
+        p = _params(N=N, H=H, Hkv=Hkv)
+        lay = _lib.AALayout()
+        assert lib.aa_workspace_layout(ctypes.byref(p), ctypes.byref(lay)) == 0
+        for name in "qkv":
+            setattr(p, name, 0x10000)
+        p.out = 0x10000
+        for t in "qkvo":
+            setattr(p, f"{t}_stride_b", H * N * 128)
+            setattr(p, f"{t}_stride_h", N * 128)
+            setattr(p, f"{t}_stride_n", 128)
+        p.workspace = 0x100000
+        p.workspace_bytes = lay.min_bytes + (lay.gather_bytes if scratch is None else scratch)
+        return lib.aa_forward_launches(ctypes.byref(p)), lay
+
+    assert count(32768, 32, 8, None)[0] == 6
+    assert count(32768, 32, 8, 0)[0] == 5
+    assert count(2048, 2, 1, None)[0] == 4                      # one big block: no candidates, no score kernel
+    n, lay = count(131072, 32, 8, None)                         # capped scratch: 8 parts of one KV head
+    assert lay.gather_bytes < 32 * (lay.ids_per_head // 128) * 65536
+    assert n == 4 + 1 + 3 * (1 + 8)
+    assert lib.aa_forward_launches(None) < 0
