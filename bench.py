@@ -351,7 +351,8 @@ def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
     aux_sparse: the labelled AUXILIARY distribution (q_shift 0.5) at 32768 tokens, where the id
     lists are sparse and step 3 runs through its gather pass: density, step times (step 3 with its
     gather pass) and TFLOP/s on the selected pairs for theta 8, 9 and 10, each from a loop of about
-    one second with the SM clock sampled.
+    one second with the SM clock sampled; and the same distribution at the benchmark's own length
+    for theta 10 (two-second loop).
     clock_normalised: step-3 SM cycles per 128-id tile and query-tile pair (launch time x median
     sampled SM clock / tile pairs / 148 SMs) for the benchmark launch and for the dense
     32768-token layer, each from a loop of about two seconds; equal cycles mean the difference in
@@ -373,6 +374,20 @@ def aux_measurements(dev, local, main_step3_ms, main_mhz, main_counts, N):
                              "sm_mhz": mhz, "gathered_tiles": call.gather_slots_used,
                              "step3_tflops_selected_pairs": 4 * D * G * cnt / (t[2] * 1e-3) / 1e12})
     del Q, K, V
+    if N > N_AUX:
+        # the same distribution at the benchmark's length, theta 10: lists that outgrow the capped gather
+        # scratch, so step 3 goes KV head by KV head (plan word 1)
+        Q, K, V = make_inputs(N, H, HKV, seed=0, rope=True, device=dev, q_shift=0.5)
+        call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, 10.0)
+        t, mhz = timed_steps(call, 2.0, local)
+        call.check_status()
+        cnt = int(call.counts.sum())
+        capN = H * sum(b * G - 2 * BLOCK for b in range(1, N // G))
+        aux["at_benchmark_length"] = {
+            "seq": N, "theta": 10.0, "density": cnt / capN, "step1_ms": t[0], "step2_ms": t[1], "step3_ms": t[2],
+            "sm_mhz": mhz, "step3_in_parts": int(call._view(call.layout.status_off, 5, torch.int32)[4]),
+            "launches": call.launches, "step3_tflops_selected_pairs": 4 * D * G * cnt / (t[2] * 1e-3) / 1e12}
+        del Q, K, V, call
     Q, K, V = make_inputs(N_AUX, H, HKV, seed=0, rope=True, device=dev)
     call = AnchorAttnCall(Q, K, V, None, BLOCK, STEP, THETA)
     t32, mhz32 = timed_steps(call, 2.0, local)
