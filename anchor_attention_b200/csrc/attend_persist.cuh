@@ -37,13 +37,13 @@
 //   step 3, list not empty: Q_A Q_B AccA_lo AccA_hi AccB_lo AccB_hi   K_0 V_0 K_1 V_1 ...
 //   step 3, empty list:             AccA_lo AccA_hi AccB_lo AccB_hi
 // (Putting K_0 among the first five entries, so that it is on its way before any entry has to be
-// released, measured slower: V_0 then waits for K_0's slot.)
+// released, measured slower on most lists: V_0 then waits for K_0's slot.)
 // Q_x is the raw query tile (a TMA box load, 128-byte swizzle): the tile's softmax warps scale and
 // round it into the CTA's query buffer, at the same offsets.  Acc?_lo / _hi are the two halves of
 // an accumulator tile in its chunk-major layout (acc_tile()): thread r reads the 16-byte chunk k
 // of its row at k * 2048 + 16 r, conflict-free.  Entries consumed by softmax warps are released
-// by them (one arrival after a named barrier over the tile's 128 threads); K/V entries by
-// tcgen05.commit, as before.
+// by them (one arrival after a named barrier over the tile's 128 threads); K/V entries by the MMA
+// warp's tcgen05.commit.
 //
 // Barrier phases run on across items: ring entries by a running entry number, score and
 // probability barriers by a running tile number, per-item barriers by the number of items with
@@ -57,8 +57,8 @@ namespace tc {
 
 struct PersistArgs {
     int qpos_n, qpos_h, qpos_b;      // query tensor map: which coordinate carries n / head / batch
-    int32_t* item_counter;           // zero before the launch
-    int n_items;
+    int32_t* item_counter;           // before the launch: the first item the launch is to take (0 when it takes all)
+    int n_items;                     // one past the last item the launch is to take
 };
 
 // what every role needs to know about one item
